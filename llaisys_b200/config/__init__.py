@@ -3,6 +3,7 @@ from .registry import config_from_dict, known_architectures, load_config, regist
 from .qwen2 import Qwen2Config
 from .vumezen import VumezenConfig
 from .nubedra import NubedraConfig
+from .zedirax import ZediraxConfig
 
-__all__ = ["CallSpec", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "SubLayerSpec", "Qwen2Config", "VumezenConfig", "NubedraConfig",
+__all__ = ["CallSpec", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "SubLayerSpec", "Qwen2Config", "VumezenConfig", "NubedraConfig", "ZediraxConfig",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

@@ -12,6 +12,8 @@
 // head instead of 0 (the term e^{sink_h}).  With `v_in_k` the values are the leading LLB_VALUE_DIM elements of the key
 // rows themselves (a cache of one latent row per token that serves as key and as value; no value pool is read).
 // `kv_row_stride` > 0: the step's own keys (and values) stand in a buffer of their own with that row stride.
+// `dist_r1`, `dist_r2` (two numbers per query head): a score loses r1 ln(1 + r2 (p - t)), a penalty that grows with the
+// distance.  `q_temp_every` > 0: the query at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / every) + 1).
 //
 // Keys are walked in tiles of one cache page with an online softmax, so nothing of size
 // [queries, keys] is ever stored.
@@ -67,6 +69,10 @@ struct AttnParams {
     const float* sink_logits;   // [nh] or null: the sink's score per query head instead of 0 (implies a sink)
     int v_in_k;           // values are the first DV elements of the key rows; vpool and v_new are not read
     int kv_row_stride;    // row stride of k_new / v_new when they are no part of the q buffer (0: row_stride)
+    const float* dist_r1; // [nh] or null: a score loses dist_r1[h] * ln(1 + dist_r2[h] * (query position - key position))
+    const float* dist_r2;
+    float q_temp_coef;    // with q_temp_every > 0 the query at position p is multiplied by
+    int q_temp_every;     //   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)
 };
 
 template <typename T, bool DECODE>
@@ -223,6 +229,14 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             if (r >= n_rows) continue;       // uniform within the warp
             int pos = DECODE ? first_pos : first_pos + r;
             int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            float row_scale = p.scale;
+            if (p.q_temp_every > 0) row_scale *= 1.0f + p.q_temp_coef * logf((float)((pos + 1) / p.q_temp_every + 1));
+            float r1 = 0.f, r2 = 0.f;
+            if (p.dist_r1) {
+                const int head = row_head0 + (DECODE ? r : 0);
+                r1 = p.dist_r1[head];
+                r2 = p.dist_r2[head];
+            }
             const float* qr = Qs + r * DH;
             const float* k0 = Ks + lane * (DH + 1);
             const float* k1 = Ks + (lane + 32) * (DH + 1);
@@ -248,8 +262,12 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             float s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]), s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
             int kp0 = tile * LLB_PAGE + lane, kp1 = kp0 + 32;
             bool v0 = (kp0 >= lo || kp0 < keep) && kp0 <= pos, v1 = (kp1 >= lo || kp1 < keep) && kp1 <= pos;
-            s0 = v0 ? s0 * p.scale : -INFINITY;
-            s1 = v1 ? s1 * p.scale : -INFINITY;
+            s0 = v0 ? s0 * row_scale : -INFINITY;
+            s1 = v1 ? s1 * row_scale : -INFINITY;
+            if (p.dist_r1) {
+                if (v0) s0 -= r1 * log1pf(r2 * (float)(pos - kp0));
+                if (v1) s1 -= r1 * log1pf(r2 * (float)(pos - kp1));
+            }
             float m_new = fmaxf(m[i], warp_max(fmaxf(s0, s1)));
             if (m_new == -INFINITY) continue;          // no visible key yet (uniform)
             float alpha = expf(m[i] - m_new);           // exp(-inf) = 0 on the first visible tile

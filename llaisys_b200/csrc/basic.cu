@@ -1032,4 +1032,214 @@ LLB_API int llb_glu(void* out, int out_dtype, const void* gate_up, int in_dtype,
     return llb_status();
 }
 
+// ------------------------------------------------------------------ stream update: scaled add, depth average, norm
+// One pass over a row of the float32 stream for arrangements whose parts join the stream scaled and whose layers hand
+// on a weighted sum of every earlier layer's result:
+//   v      = cur[r] + delta_scale * sum_p delta[p][r]                (delta optional; written back to cur with write_back)
+//   y      = mix ? sum_{j < n-1} mix[j] * X_j[r] + mix[n-1] * v : v   (X_0 = x0, X_j = planes + (j-1) * plane_stride for j >= 1;
+//                                                                     the last of the n terms is the row just formed)
+//   dst[r] = y                                                        (dst optional: the plane the next layer works on)
+//   out[r] = y / sqrt(mean(y^2) + eps) * weight                       (out optional)
+// With `rows` only the rows listed there are read, nothing is written back, and dst and out are [len(rows), H].
+// Terms are added in ascending j, so a row's result does not depend on what else the step holds.
+struct StreamUpdateParams {
+    float* cur;               // [T, H] the row's current plane
+    const void* delta;        // [n_part, T, H] or null
+    int n_part;
+    long long part_stride;
+    float delta_scale;
+    int write_back;
+    const float* mix;         // [n] or null
+    int n;                    // terms of the sum
+    const float* x0;          // [T, H]
+    const float* planes;      // [n - 2 planes of T * H ahead of cur's]
+    long long plane_stride;
+    float* dst;               // [R, H] or null
+    const void* weight;       // [H]
+    void* out;                // [R, H] or null
+    const int* rows;          // [R] or null
+    int H;
+    float eps;
+};
+
+template <typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(256) stream_update_kernel(StreamUpdateParams p) {
+    extern __shared__ float rowbuf[];
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5, H = p.H;
+    llb_grid_dependency_sync();
+    const size_t src = p.rows ? (size_t)p.rows[r] : (size_t)r;
+    float* cur = p.cur + src * H;
+    const TD* delta = (const TD*)p.delta;
+    float ss = 0.f;
+    for (int j = tid; j < H; j += 256) {
+        float v = cur[j];
+        if (delta) {
+            float d = 0.f;
+            for (int q = 0; q < p.n_part; ++q) d += to_f32(delta[(size_t)q * p.part_stride + src * H + j]);
+            v = fmaf(p.delta_scale, d, v);
+            if (p.write_back) cur[j] = v;
+        }
+        if (p.mix) {
+            float acc = 0.f;
+            if (p.n > 1) acc = p.mix[0] * p.x0[src * H + j];
+            for (int k = 1; k + 1 < p.n; ++k) acc = fmaf(p.mix[k], p.planes[(size_t)(k - 1) * p.plane_stride + src * H + j], acc);
+            v = fmaf(p.mix[p.n - 1], v, acc);
+        }
+        if (p.dst) p.dst[(size_t)r * H + j] = v;
+        rowbuf[j] = v;
+        ss += v * v;
+    }
+    if (!p.out) return;
+    ss = warp_sum(ss);
+    if (lane == 0) red[wp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + p.eps);
+    const TW* w = (const TW*)p.weight;
+    TO* out = (TO*)p.out + (size_t)r * H;
+    for (int j = tid; j < H; j += 256) out[j] = from_f32<TO>(rowbuf[j] * inv * to_f32(w[j]));
+}
+
+// The same with 16-byte accesses to the float32 planes (8-byte ones to bfloat16 operands): widths that are multiples
+// of 4, aligned bases.  Sums are formed in the same order as above.
+template <typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(256) stream_update_vec_kernel(StreamUpdateParams p) {
+    extern __shared__ float rowbuf[];
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5, H = p.H, H4 = H >> 2;
+    llb_grid_dependency_sync();
+    const size_t src = p.rows ? (size_t)p.rows[r] : (size_t)r;
+    float* cur = p.cur + src * H;
+    const TD* delta = (const TD*)p.delta;
+    float ss = 0.f;
+    for (int g = tid; g < H4; g += 256) {
+        const int j = g * 4;
+        const float4 c4 = *reinterpret_cast<const float4*>(cur + j);
+        float v[4] = {c4.x, c4.y, c4.z, c4.w};
+        if (delta) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < p.n_part; ++q) {
+                const TD* dp = delta + (size_t)q * p.part_stride + src * H + j;
+                if (sizeof(TD) == 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(dp);
+                    d[0] += t.x; d[1] += t.y; d[2] += t.z; d[3] += t.w;
+                } else {
+                    const uint2 t = *reinterpret_cast<const uint2*>(dp);
+                    const TD* e = reinterpret_cast<const TD*>(&t);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) d[u] += to_f32(e[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = fmaf(p.delta_scale, d[u], v[u]);
+            if (p.write_back) *reinterpret_cast<float4*>(cur + j) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        if (p.mix) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p.n > 1) {
+                const float a = p.mix[0];
+                const float4 t = *reinterpret_cast<const float4*>(p.x0 + src * H + j);
+                acc[0] = a * t.x; acc[1] = a * t.y; acc[2] = a * t.z; acc[3] = a * t.w;
+            }
+            for (int k = 1; k + 1 < p.n; ++k) {
+                const float a = p.mix[k];
+                const float4 t = *reinterpret_cast<const float4*>(p.planes + (size_t)(k - 1) * p.plane_stride + src * H + j);
+                acc[0] = fmaf(a, t.x, acc[0]); acc[1] = fmaf(a, t.y, acc[1]); acc[2] = fmaf(a, t.z, acc[2]); acc[3] = fmaf(a, t.w, acc[3]);
+            }
+            const float a = p.mix[p.n - 1];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = fmaf(a, v[u], acc[u]);
+        }
+        if (p.dst) *reinterpret_cast<float4*>(p.dst + (size_t)r * H + j) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(rowbuf + j) = make_float4(v[0], v[1], v[2], v[3]);
+        ss += (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
+    }
+    if (!p.out) return;
+    ss = warp_sum(ss);
+    if (lane == 0) red[wp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + p.eps);
+    const TW* w = (const TW*)p.weight;
+    TO* out = (TO*)p.out + (size_t)r * H;
+    for (int g = tid; g < H4; g += 256) {
+        const int j = g * 4;
+        const float4 x = *reinterpret_cast<const float4*>(rowbuf + j);
+        const float y[4] = {x.x * inv * to_f32(w[j]), x.y * inv * to_f32(w[j + 1]), x.z * inv * to_f32(w[j + 2]), x.w * inv * to_f32(w[j + 3])};
+        if (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(out + j) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+            uint2 o;
+            TO* e = reinterpret_cast<TO*>(&o);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = from_f32<TO>(y[u]);
+            *reinterpret_cast<uint2*>(out + j) = o;
+        }
+    }
+}
+
+LLB_API int llb_stream_update(StreamUpdateParams p, int delta_dtype, int w_dtype, int out_dtype, int R, cudaStream_t stream) {
+    if (R == 0) return 0;
+    const size_t smem = (size_t)p.H * sizeof(float);
+    if (smem > 200 * 1024 || (p.mix && p.n < 1) || (p.rows && p.write_back)) return (int)cudaErrorInvalidValue;
+    if (!p.delta) delta_dtype = LLB_F32;
+    if (!p.out) { out_dtype = LLB_F32; w_dtype = LLB_F32; }
+    const bool vec = p.H % 4 == 0 && p.part_stride % 4 == 0 && p.plane_stride % 4 == 0 &&
+                     !(((uintptr_t)p.cur | (uintptr_t)p.delta | (uintptr_t)p.x0 | (uintptr_t)p.planes | (uintptr_t)p.dst | (uintptr_t)p.out) & 15);
+    LLB_DISPATCH_DTYPE(delta_dtype, TD, {
+        LLB_DISPATCH_DTYPE(w_dtype, TW, {
+            LLB_DISPATCH_DTYPE(out_dtype, TO, {
+                auto k = vec ? stream_update_vec_kernel<TD, TW, TO> : stream_update_kernel<TD, TW, TO>;
+                if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                llb_launch(k, dim3(R), dim3(256), smem, stream, p);
+            });
+        });
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ activation of rows, with a factor per row
+// x[t, :cols] <- act(x[t, :cols]) * factor_t in place (row stride ldx), factor_t = scale * sigmoid(logit[t * ld_logit])
+// (scale alone without logits); act 1: max(., 0)^2, 2: gelu (erf form), 3: gelu (tanh form).  float32 arithmetic, one rounding.
+__device__ __forceinline__ float row_act(float v, int act) {
+    if (act == 1) { v = fmaxf(v, 0.f); return v * v; }
+    if (act == 2) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) act_rows_kernel(T* __restrict__ x, int ldx, int cols, int act, const float* __restrict__ logit,
+                                                       int ld_logit, float scale) {
+    const int t = blockIdx.x;
+    llb_grid_dependency_sync();
+    const float f = logit ? scale / (1.0f + expf(-logit[(size_t)t * ld_logit])) : scale;
+    T* row = x + (size_t)t * ldx;
+    constexpr int VEC = 16 / (int)sizeof(T);
+    if (cols % VEC == 0 && ldx % VEC == 0 && !((uintptr_t)x & 15)) {
+        for (int g = threadIdx.x; g < cols / VEC; g += 256) {
+            uint4 v = reinterpret_cast<uint4*>(row)[g];
+            T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) e[u] = from_f32<T>(row_act(to_f32(e[u]), act) * f);
+            reinterpret_cast<uint4*>(row)[g] = v;
+        }
+        return;
+    }
+    for (int j = threadIdx.x; j < cols; j += 256) row[j] = from_f32<T>(row_act(to_f32(row[j]), act) * f);
+}
+
+LLB_API int llb_act_rows(void* x, int dtype, int T, int ldx, int cols, int act, const float* logit, int ld_logit, float scale,
+                         cudaStream_t stream) {
+    if (T == 0 || cols == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT,
+        llb_launch(act_rows_kernel<TT>, dim3(T), dim3(256), 0, stream, (TT*)x, ldx, cols, act, logit, ld_logit, scale));
+    return llb_status();
+}
+
 LLB_API const char* llb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

@@ -9,7 +9,8 @@
 //  * latent_prep: per token, from the fused down projections: RMS norm (plain weight) of the query latent; RMS norm
 //    of the key/value latent; rotation of the shared key part (pairs (2i, 2i+1), angles from float32 tables that
 //    already hold any rescaling of frequency and magnitude); the row [c | rotated part] is written densely for the
-//    step's attention and, with `append`, into the token's row of the paged cache.
+//    step's attention and, with `append`, into the token's row of the paged cache.  With `halves` the rotated pairs
+//    are (i, i + rot/2) instead (here and in the two kernels below).
 //  * latent_append: the same rows into the paged cache as a pass of its own (a ring cache is appended to after the
 //    step's attention).
 //  * head_matmul: y[t, h, :] = x[t, h, :] M[h]  (M [heads, in, out]) with float32 accumulation: the query's unrotated
@@ -42,6 +43,7 @@ struct LatentPrepParams {
     const int* page_table;
     int table_stride, ring, pinned;
     int* err;
+    int halves;               // rotated pairs are (i, i + rot / 2) instead of (2i, 2i + 1)
 };
 
 template <typename T, typename TW>
@@ -55,8 +57,8 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(LatentPrepParams p) {
     }
     llb_grid_dependency_sync();
     const T* row = (const T*)p.proj + (size_t)t * p.row_stride;
-    // ---- the query latent
-    {
+    // ---- the query latent (q_rank 0: the layer's queries pass through none)
+    if (p.q_rank > 0) {
         float ss = 0.f;
         for (int j = tid; j < p.q_rank; j += 256) {
             float v = to_f32(row[p.q_off + j]);
@@ -106,13 +108,14 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(LatentPrepParams p) {
     const int half = p.rot >> 1;
     for (int i = tid; i < half; i += 256) {
         const float c = p.cos_t[(size_t)pos * half + i], s = p.sin_t[(size_t)pos * half + i];
-        const float a = to_f32(row[p.kr_off + 2 * i]), b = to_f32(row[p.kr_off + 2 * i + 1]);
+        const int ia = p.halves ? i : 2 * i, ib = p.halves ? i + half : 2 * i + 1;
+        const float a = to_f32(row[p.kr_off + ia]), b = to_f32(row[p.kr_off + ib]);
         T x = from_f32<T>(a * c - b * s), y = from_f32<T>(b * c + a * s);
-        dense[p.kv_rank + 2 * i] = x;
-        dense[p.kv_rank + 2 * i + 1] = y;
+        dense[p.kv_rank + ia] = x;
+        dense[p.kv_rank + ib] = y;
         if (paged) {
-            paged[p.kv_rank + 2 * i] = x;
-            paged[p.kv_rank + 2 * i + 1] = y;
+            paged[p.kv_rank + ia] = x;
+            paged[p.kv_rank + ib] = y;
         }
     }
     for (int j = p.rot + tid; j < p.rope_dim; j += 256) {
@@ -184,6 +187,8 @@ struct HeadMatmulParams {
     const void* gate;
     int gate_stride;
     int* err;
+    int halves;               // rotated pairs are (i, i + rot / 2) instead of (2i, 2i + 1)
+    int gate_elems;           // the gate has a value per output element (at h * n_out + column) instead of one per head
 };
 
 template <typename T>
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(HM_THREADS) head_matmul_kernel(HeadMatmulParam
             float v = (part[t * HM_COLS + lane] + part[(HM_TOK + t) * HM_COLS + lane]) +
                       (part[(2 * HM_TOK + t) * HM_COLS + lane] + part[(3 * HM_TOK + t) * HM_COLS + lane]);
             if (p.gate) {
-                float g = to_f32(((const T*)p.gate)[(size_t)(t0 + t) * p.gate_stride + h]);
+                float g = to_f32(((const T*)p.gate)[(size_t)(t0 + t) * p.gate_stride + (p.gate_elems ? h * p.n_out + min(col, p.n_out - 1) : h)]);
                 v *= 1.0f / (1.0f + expf(-g));
             }
             if (col < p.n_out) yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + col] = from_f32<T>(v);
@@ -263,9 +268,10 @@ __global__ void __launch_bounds__(HM_THREADS) head_matmul_kernel(HeadMatmulParam
             const float c = p.cos_t[(size_t)pos * half + j], s = p.sin_t[(size_t)pos * half + j];
             const T* src = xb + (size_t)(t0 + t) * p.x_stride + h * p.x_head + p.n_in;
             T* dst = yb + (size_t)(t0 + t) * p.y_stride + h * p.y_head + p.n_out;
-            const float a = to_f32(src[2 * j]), b = to_f32(src[2 * j + 1]);
-            dst[2 * j] = from_f32<T>(a * c - b * s);
-            dst[2 * j + 1] = from_f32<T>(b * c + a * s);
+            const int ia = p.halves ? j : 2 * j, ib = p.halves ? j + half : 2 * j + 1;
+            const float a = to_f32(src[ia]), b = to_f32(src[ib]);
+            dst[ia] = from_f32<T>(a * c - b * s);
+            dst[ib] = from_f32<T>(b * c + a * s);
         }
         const int rest = p.tail - p.rot;
         for (int i = tid; i < nt * rest; i += HM_THREADS) {
@@ -295,7 +301,7 @@ LLB_API int llb_head_matmul(HeadMatmulParams p, int dtype, cudaStream_t stream) 
 template <typename T>
 __global__ void __launch_bounds__(128) rope_pairs_kernel(T* __restrict__ x, int stride, int H, int head, int off, int rot,
                                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                                         int table_rows, const int* __restrict__ tok_pos, int* err) {
+                                                         int table_rows, const int* __restrict__ tok_pos, int* err, int halves) {
     const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
     if (pos < 0 || pos >= table_rows) {
         if (threadIdx.x == 0) atomicExch(err, 2);
@@ -306,19 +312,20 @@ __global__ void __launch_bounds__(128) rope_pairs_kernel(T* __restrict__ x, int 
     for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
         const int h = i / half, j = i - h * half;
         const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
-        T* e = row + h * head + off + 2 * j;
-        const float a = to_f32(e[0]), b = to_f32(e[1]);
-        e[0] = from_f32<T>(a * c - b * s);
-        e[1] = from_f32<T>(b * c + a * s);
+        T* ea = row + h * head + off + (halves ? j : 2 * j);
+        T* eb = row + h * head + off + (halves ? j + half : 2 * j + 1);
+        const float a = to_f32(*ea), b = to_f32(*eb);
+        *ea = from_f32<T>(a * c - b * s);
+        *eb = from_f32<T>(b * c + a * s);
     }
 }
 
 LLB_API int llb_rope_pairs(void* x, int dtype, int T, int stride, int H, int head, int off, int rot, const float* cos_t,
-                           const float* sin_t, int table_rows, const int* tok_pos, int* err, cudaStream_t stream) {
+                           const float* sin_t, int table_rows, const int* tok_pos, int* err, int halves, cudaStream_t stream) {
     if (T == 0 || rot <= 0) return 0;
     LLB_DISPATCH_DTYPE(dtype, TT, {
         llb_launch(rope_pairs_kernel<TT>, dim3(T), dim3(128), 0, stream, (TT*)x, stride, H, head, off, rot, cos_t, sin_t,
-                   table_rows, tok_pos, err);
+                   table_rows, tok_pos, err, halves);
     });
     return llb_status();
 }

@@ -3,7 +3,8 @@
 //
 //   select   from the router's logits z = Wr h (float32): g = 1 / (1 + e^-z); the `top` experts with the largest
 //            g + bias are chosen (ties go to the lower index); a chosen expert's weight is g * route_scale, not
-//            renormalised.
+//            renormalised.  Mode 1: the largest logits z + bias are chosen and the weights are the softmax over the
+//            chosen logits only, times route_scale.
 //   plan     pair i = (token i / top, choice i % top).  Pairs are grouped by expert: slot_of[pair] is a pair's place
 //            in that order, pair_of[slot] its inverse, and every expert's run of slots is cut into tiles of
 //            `tile_rows` rows (tile -> expert, first slot, rows), so that the products run over a grid whose size
@@ -21,7 +22,7 @@ constexpr int MOE_TILE = 64;
 // arg-max (ties to the lower index), weights g * route_scale.
 __global__ void __launch_bounds__(128)
 moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int T, int E, int top, float route_scale,
-                  int* __restrict__ idx, float* __restrict__ wgt) {
+                  int* __restrict__ idx, float* __restrict__ wgt, int mode) {
     extern __shared__ float sm[];                 // per warp: gate[E], choice[E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
@@ -30,7 +31,8 @@ moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
     llb_grid_dependency_sync();
     if (t >= T) return;
     for (int e = lane; e < E; e += 32) {
-        const float g = 1.0f / (1.0f + expf(-z[(size_t)t * ldz + e]));
+        const float zl = z[(size_t)t * ldz + e];
+        const float g = mode == 1 ? zl : 1.0f / (1.0f + expf(-zl));
         gate[e] = g;
         choice[e] = g + (bias ? bias[e] : 0.f);
     }
@@ -54,20 +56,34 @@ moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
         }
         if (lane == 0) {
             idx[(size_t)t * top + k] = arg;
-            wgt[(size_t)t * top + k] = gate[arg] * route_scale;
+            wgt[(size_t)t * top + k] = mode == 1 ? gate[arg] : gate[arg] * route_scale;
             choice[arg] = -INFINITY;
         }
         __syncwarp();
     }
+    if (mode == 1 && lane == 0) {
+        // softmax over the chosen logits only, in the order they were chosen
+        float* w = wgt + (size_t)t * top;
+        float mx = -INFINITY;
+        for (int k = 0; k < top; ++k) mx = fmaxf(mx, w[k]);
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float ex = expf(w[k] - mx);
+            w[k] = ex;
+            sum += ex;
+        }
+        const float inv = route_scale / sum;
+        for (int k = 0; k < top; ++k) w[k] *= inv;
+    }
 }
 
 LLB_API int llb_moe_select(const float* z, int ldz, const float* bias, int T, int E, int top, float route_scale, int* idx,
-                           float* wgt, cudaStream_t stream) {
+                           float* wgt, int mode, cudaStream_t stream) {
     if (T == 0) return 0;
     if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)4 * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    llb_launch(moe_select_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, z, ldz, bias, T, E, top, route_scale, idx, wgt);
+    llb_launch(moe_select_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, z, ldz, bias, T, E, top, route_scale, idx, wgt, mode);
     return llb_status();
 }
 
@@ -143,7 +159,7 @@ LLB_API int llb_moe_tile_rows() { return MOE_TILE; }
 
 // ------------------------------------------------------------------ the experts' products on the CUDA cores
 // out[slot, n] = act(sum_k A[row(slot), k] W[expert][n, k]) for the slots of one tile; row(slot) = pair_of[slot] / top
-// when the rows are gathered from the tokens (GATHER), else slot itself.  ACT 1: max(., 0)^2.
+// when the rows are gathered from the tokens (GATHER), else slot itself.  ACT 1: max(., 0)^2; 2: gelu (erf form).
 template <typename TA, typename TW, typename TO, bool GATHER, int ACT>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ pair_of, int top, const TW* __restrict__ W,
@@ -204,13 +220,14 @@ moe_gemm_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ pair_
                 v = fmaxf(v, 0.f);
                 v = v * v;
             }
+            if (ACT == 2) v = 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
             out[(size_t)(slot0 + r) * ldo + n] = from_f32<TO>(v);
         }
     }
 }
 
 // gather != 0: A is the tokens' activations [T, lda] and a slot's row is its pair's token; else A is [slots, lda].
-// act 1: squared ReLU.  W is the experts' matrices stacked, [E, N, K].
+// act 1: squared ReLU, 2: gelu (erf form).  W is the experts' matrices stacked, [E, N, K].
 LLB_API int llb_moe_gemm(const void* A, int a_dtype, int lda, const int* pair_of, int top, int gather, const void* W,
                          int w_dtype, void* out, int o_dtype, int ldo, const int* tiles, int max_tiles, const int* n_tiles,
                          int N, int K, int act, cudaStream_t stream) {
@@ -224,8 +241,10 @@ LLB_API int llb_moe_gemm(const void* A, int a_dtype, int lda, const int* pair_of
         LLB_DISPATCH_DTYPE(w_dtype, TW, {
             LLB_DISPATCH_DTYPE(o_dtype, TO, {
                 if (gather && act == 1) LLB_MG(true, 1);
+                else if (gather && act == 2) LLB_MG(true, 2);
                 else if (gather) LLB_MG(true, 0);
                 else if (act == 1) LLB_MG(false, 1);
+                else if (act == 2) LLB_MG(false, 2);
                 else LLB_MG(false, 0);
             });
         });

@@ -12,7 +12,7 @@
 //
 //   TMA (128-byte swizzle) -> ring of STAGES k-blocks -> tcgen05.mma by one elected lane, accumulator in tensor memory
 //   -> tcgen05.ld by four warps -> the epilogue:
-//        store         out[slot, n] = act(acc)                     (act: none or max(., 0)^2)
+//        store         out[slot, n] = act(acc)                     (act: none, max(., 0)^2 or gelu, erf form)
 //        weighted add  stream[token(slot), n] += weight(slot) * acc   (float32 atomics: a token's chosen experts and
 //                      the layer's other branches meet in the stream in arrival order)
 //
@@ -35,7 +35,7 @@ struct Shape {                          // two blocks share an SM: under 113 KB 
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
 enum { ERR_MOE_WAIT_FULL = 151, ERR_MOE_WAIT_EMPTY = 152, ERR_MOE_WAIT_ACC = 153 };
-enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_WEIGHTED_ADD = 2 };
+enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_WEIGHTED_ADD = 2, EPI_GELU = 3 };
 
 struct MoeTcArgs {
     void* out;                 // store: [slots, ldo] bfloat16 or float32; weighted add: the float32 stream [T, ldo]
@@ -178,6 +178,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         x = fmaxf(x, 0.f);
                         x *= x;
                     }
+                    if (g.epilogue == EPI_GELU) x = 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
                     const size_t o = (size_t)(slot0 + c + j) * g.ldo + n;
                     if (g.out_dtype == LLB_F32) ((float*)g.out)[o] = x;
                     else ((bf16*)g.out)[o] = __float2bfloat16_rn(x);
@@ -211,7 +212,7 @@ static int launch_moe_tc(const CUtensorMap& mw, const CUtensorMap& mx, const Moe
 }
 
 // A [slots, K] bfloat16 (row stride lda) in slot order; W [E, N, K] bfloat16, dense; tiles of tile_rows (16, 64 or 128)
-// slots as the plan cut them.  epilogue 0: out[slots, ldo] = product; 1: its squared ReLU; 2: out is the float32 stream
+// slots as the plan cut them.  epilogue 0: out[slots, ldo] = product; 1: its squared ReLU; 3: its gelu (erf form); 2: out is the float32 stream
 // [T, ldo] and row token(slot) gets weight(slot) * product added.  K must be a multiple of 8 and all bases 16-byte aligned.
 LLB_API int llb_moe_gemm_tc(const void* A, int lda, long long n_slots, const void* W, int E, int N, int K, void* out, int out_dtype,
                             int ldo, const int* tiles, int max_tiles, const int* n_tiles, int tile_rows, int epilogue,
@@ -219,7 +220,7 @@ LLB_API int llb_moe_gemm_tc(const void* A, int lda, long long n_slots, const voi
     const int BN = tile_rows;
     if (BN != 16 && BN != 64 && BN != 128) return (int)cudaErrorInvalidValue;
     if (max_tiles == 0 || N == 0 || n_slots == 0) return 0;
-    if (K % 8 || lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || epilogue < 0 || epilogue > 2) return (int)cudaErrorInvalidValue;
+    if (K % 8 || lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || epilogue < 0 || epilogue > 3) return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_WEIGHTED_ADD && (!pair_of || !wgt || top < 1 || out_dtype != LLB_F32)) return (int)cudaErrorInvalidValue;
     if (out_dtype != LLB_F32 && out_dtype != LLB_BF16) return (int)cudaErrorInvalidValue;
     dim3 grid((N + BM - 1) / BM, max_tiles);

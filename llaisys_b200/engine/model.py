@@ -85,6 +85,8 @@ class DecoderModel:
     def parts(self) -> List[Part]:
         ps: List[Part] = [self.embedding]
         for b in self.blocks:
+            if b.spec is not None:                   # an arrangement with tensors of its own
+                ps.append(b)
             for sub in b.sublayers:
                 ps += ([sub.norm] if sub.norm is not None else []) + [sub.part]
                 ps += [sub.post_norm] if sub.post_norm is not None else []

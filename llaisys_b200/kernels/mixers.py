@@ -64,44 +64,86 @@ def gla_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, H: int, d
     return out
 
 
+class _MinGruParams(ctypes.Structure):
+    _fields_ = [("proj", c_void_p), ("ld", c_int), ("a_off", c_int), ("u_off", c_int), ("g_off", c_int), ("width", c_int),
+                ("state", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("out", c_void_p), ("chunk_a", c_void_p),
+                ("chunk_b", c_void_p), ("chunk", c_int), ("n_chunks", c_int)]
+
+
+MINGRU_CHUNK = 64            # tokens of a chunk of a long step (256 beyond 4,096 tokens a sequence)
+
+
+def mingru(proj: torch.Tensor, width: int, state: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+           max_new: int, out_dtype: torch.dtype, offsets=None) -> torch.Tensor:
+    """The minGRU recurrence over the new tokens of every sequence: proj [T, >= 3 width] holds the gate logits, the
+    candidate inputs and the output gate (`offsets` = their first columns, default 0, width, 2 width), biases included;
+    state [slots, width] (float32) is read at row seq_slot[b] and left holding the state after the step.  Returns
+    y [T, width] = state_t * silu(output gate) in out_dtype.  Steps of more than one chunk of tokens a sequence are cut
+    into chunks that run side by side (three launches instead of one)."""
+    _need_cuda(proj, state)
+    assert proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width
+    T = proj.shape[0]
+    a_off, u_off, g_off = offsets or (0, width, 2 * width)
+    out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    p = _MinGruParams()
+    p.proj, p.ld, p.a_off, p.u_off, p.g_off, p.width = proj.data_ptr(), proj.stride(0), a_off, u_off, g_off, width
+    p.state, p.seq_start, p.seq_slot, p.out = state.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(), out.data_ptr()
+    p.chunk = MINGRU_CHUNK if max_new <= 4096 else 256
+    p.n_chunks = -(-max_new // p.chunk)
+    scratch, launches = None, 1
+    if p.n_chunks > 1:
+        scratch = torch.empty((2, n_seqs, p.n_chunks, width), dtype=torch.float32, device=proj.device)
+        p.chunk_a, p.chunk_b = scratch[0].data_ptr(), scratch[1].data_ptr()
+        launches = 3
+    f = _fn(load_module("mingru.cu"), "llb_mingru", [_MinGruParams, c_int, c_int, c_int, c_void_p])
+    _check(f(p, _dt(proj), DT[out_dtype], n_seqs, _stream()), "minGRU recurrence", launches)
+    del scratch
+    return out
+
+
 class _LatentPrepParams(ctypes.Structure):
     _fields_ = [("proj", c_void_p), ("row_stride", c_int), ("q_off", c_int), ("q_rank", c_int), ("kv_off", c_int),
                 ("kv_rank", c_int), ("kr_off", c_int), ("rope_dim", c_int), ("rot", c_int), ("wq", c_void_p), ("wkv", c_void_p),
                 ("eps", c_float), ("cos_t", c_void_p), ("sin_t", c_void_p), ("table_rows", c_int), ("tok_pos", c_void_p),
                 ("q_out", c_void_p), ("kv_out", c_void_p), ("append", c_int), ("tok_seq", c_void_p), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("pool", c_void_p), ("page_table", c_void_p), ("table_stride", c_int),
-                ("ring", c_int), ("pinned", c_int), ("err", c_void_p)]
+                ("ring", c_int), ("pinned", c_int), ("err", c_void_p), ("halves", c_int)]
 
 
-def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rope_dim: int, wq: torch.Tensor, wkv: Optional[torch.Tensor],
-                eps: float, tables, tok_pos: torch.Tensor, err: torch.Tensor, append: Optional[dict] = None):
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rope_dim: int, wq: Optional[torch.Tensor], wkv: Optional[torch.Tensor],
+                eps: float, tables, tok_pos: torch.Tensor, err: torch.Tensor, append: Optional[dict] = None, halves: bool = False,
+                kv_off: Optional[int] = None):
     """From the fused down projections proj [T, q_rank (+ kv_rank + rope_dim) ...]: the RMS-normed query latent
     [T, q_rank] and, when the layer projects its own (wkv given), the rows [normed latent | rotated shared key part]
     [T, kv_rank + rope_dim]; tables = (cos, sin, rotated dims) or None.  append = dict(tok_seq, seq_start,
-    seq_len_before, pool, page_table, ring, pinned) also writes those rows into the paged cache."""
+    seq_len_before, pool, page_table, ring, pinned) also writes those rows into the paged cache.  halves: the rotated
+    pairs are (i, i + dims / 2) instead of (2i, 2i + 1).  q_rank 0 (wq None): the layer has no query latent; kv_off then
+    says where the key/value latent's columns start (default: after the query latent)."""
     _need_cuda(proj, wq, wkv, tok_pos)
     T = proj.shape[0]
     assert proj.stride(1) == 1 and tok_pos.numel() == T
     own = wkv is not None
-    q_out = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    assert (q_rank > 0) == (wq is not None) and (own or q_rank > 0)
+    q_out = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
     kv_out = torch.empty((T, kv_rank + rope_dim), dtype=proj.dtype, device=proj.device) if own else None
     p = _LatentPrepParams()
     p.proj, p.row_stride, p.q_off, p.q_rank = proj.data_ptr(), proj.stride(0), 0, q_rank
-    p.kv_off, p.kv_rank, p.kr_off, p.rope_dim = q_rank, kv_rank if own else 0, q_rank + kv_rank, rope_dim
-    p.wq, p.wkv, p.eps = wq.data_ptr(), _ptr(wkv), eps
-    if own and wkv.dtype != wq.dtype:
+    off = q_rank if kv_off is None else int(kv_off)
+    p.kv_off, p.kv_rank, p.kr_off, p.rope_dim = off, kv_rank if own else 0, off + kv_rank, rope_dim
+    p.wq, p.wkv, p.eps, p.halves = _ptr(wq), _ptr(wkv), eps, int(halves)
+    if own and wq is not None and wkv.dtype != wq.dtype:
         raise KernelError("latent_prep: the two norm weights must have one dtype")
     if tables is not None and own:
         cos, sin, rot = tables
         p.cos_t, p.sin_t, p.table_rows, p.rot = cos.data_ptr(), sin.data_ptr(), cos.shape[0], rot
-    p.tok_pos, p.q_out, p.kv_out, p.err = tok_pos.data_ptr(), q_out.data_ptr(), _ptr(kv_out), err.data_ptr()
+    p.tok_pos, p.q_out, p.kv_out, p.err = tok_pos.data_ptr(), _ptr(q_out), _ptr(kv_out), err.data_ptr()
     if append is not None and own:
         a = append
         p.append, p.tok_seq, p.seq_start, p.seq_len_before = 1, a["tok_seq"].data_ptr(), a["seq_start"].data_ptr(), a["seq_len_before"].data_ptr()
         p.pool, p.page_table, p.table_stride = a["pool"].data_ptr(), a["page_table"].data_ptr(), a["page_table"].shape[1]
         p.ring, p.pinned = a["ring"], a.get("pinned", 0)
     f = _fn(load_module("latent.cu"), "llb_latent_prep", [_LatentPrepParams, c_int, c_int, c_int, c_void_p])
-    _check(f(p, _dt(proj), _dt(wq), T, _stream()), "latent attention (norms, key rotation, cache rows)")
+    _check(f(p, _dt(proj), _dt(wq if wq is not None else wkv), T, _stream()), "latent attention (norms, key rotation, cache rows)")
     return q_out, kv_out
 
 
@@ -121,15 +163,16 @@ class _HeadMatmulParams(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("x_stride", c_int), ("x_head", c_int), ("m", c_void_p), ("y", c_void_p), ("y_stride", c_int),
                 ("y_head", c_int), ("T", c_int), ("H", c_int), ("n_in", c_int), ("n_out", c_int), ("tail", c_int), ("rot", c_int),
                 ("cos_t", c_void_p), ("sin_t", c_void_p), ("table_rows", c_int), ("tok_pos", c_void_p), ("gate", c_void_p),
-                ("gate_stride", c_int), ("err", c_void_p)]
+                ("gate_stride", c_int), ("err", c_void_p), ("halves", c_int), ("gate_elems", c_int)]
 
 
 def head_matmul(x: torch.Tensor, m: torch.Tensor, *, tail: int = 0, tables=None, tok_pos=None, gate: Optional[torch.Tensor] = None,
-                err: Optional[torch.Tensor] = None) -> torch.Tensor:
+                err: Optional[torch.Tensor] = None, halves: bool = False, gate_elems: bool = False) -> torch.Tensor:
     """y[t, h, :n_out] = x[t, h, :n_in] m[h] for x [T, H (n_in + tail)] and m [H, n_in, n_out], float32 accumulation; the
     `tail` elements after a head's inputs follow its outputs in y [T, H (n_out + tail)], the first `rot` of them rotated in
     pairs (2i, 2i+1) by tables = (cos, sin, rot) at the tokens' positions; with gate ([T, >= H] view) every head's
-    outputs are multiplied by sigmoid(gate[t, h])."""
+    outputs are multiplied by sigmoid(gate[t, h]), or, with gate_elems, output element i of head h by
+    sigmoid(gate[t, h n_out + i]) (gate a [T, >= H n_out] view).  halves: the rotated pairs are (i, i + rot / 2)."""
     _need_cuda(x, m, gate, tok_pos)
     T = x.shape[0]
     H, n_in, n_out = m.shape
@@ -139,6 +182,7 @@ def head_matmul(x: torch.Tensor, m: torch.Tensor, *, tail: int = 0, tables=None,
     p.x, p.x_stride, p.x_head, p.m = x.data_ptr(), x.stride(0), n_in + tail, m.data_ptr()
     p.y, p.y_stride, p.y_head = y.data_ptr(), y.stride(0), n_out + tail
     p.T, p.H, p.n_in, p.n_out, p.tail = T, H, n_in, n_out, tail
+    p.halves, p.gate_elems = int(halves), int(gate_elems)
     if tail and tables is not None:
         cos, sin, rot = tables
         if tok_pos is None or err is None:
@@ -152,18 +196,19 @@ def head_matmul(x: torch.Tensor, m: torch.Tensor, *, tail: int = 0, tables=None,
     return y
 
 
-def rope_pairs_(x: torch.Tensor, H: int, head: int, off: int, tables, tok_pos: torch.Tensor, err: torch.Tensor) -> None:
-    """In place on x [T, >= H head] (row stride free): of every head's elements from `off` on, the pairs (2i, 2i+1),
-    i < rot / 2, are rotated by tables = (cos, sin, rot) at the tokens' positions."""
+def rope_pairs_(x: torch.Tensor, H: int, head: int, off: int, tables, tok_pos: torch.Tensor, err: torch.Tensor,
+                halves: bool = False) -> None:
+    """In place on x [T, >= H head] (row stride free): of every head's elements from `off` on, the pairs (2i, 2i+1)
+    (with halves: (i, i + rot / 2)), i < rot / 2, are rotated by tables = (cos, sin, rot) at the tokens' positions."""
     _need_cuda(x, tok_pos)
     if tables is None:
         return
     cos, sin, rot = tables
     assert x.stride(1) == 1 and off + rot <= head
     f = _fn(load_module("latent.cu"), "llb_rope_pairs", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                                         c_int, c_void_p, c_void_p, c_void_p])
+                                                         c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(x), _dt(x), x.shape[0], x.stride(0), H, head, off, rot, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_pos), _ptr(err),
-             _stream()), "rotation of neighbouring pairs")
+             int(halves), _stream()), "rotation of pairs")
 
 
 def head_gate_(x: torch.Tensor, gate: torch.Tensor, H: int) -> torch.Tensor:

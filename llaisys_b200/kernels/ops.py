@@ -175,6 +175,78 @@ def relu_squared_(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
+ROW_ACTS = {None: 0, "relu_squared": 1, "gelu": 2, "gelu_tanh": 3}
+
+
+def act_rows_(x: torch.Tensor, act: Optional[str], logit: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """In place on x [T, cols] (row stride free): x[t] <- act(x[t]) * scale * sigmoid(logit[t]) (scale alone without
+    `logit`, a float32 [T] view with any stride); act None, "relu_squared", "gelu" (erf form) or "gelu_tanh"."""
+    _need_cuda(x, logit)
+    assert x.dim() == 2 and x.stride(1) == 1
+    if logit is not None:
+        assert logit.dtype == torch.float32 and logit.dim() == 1 and logit.numel() == x.shape[0]
+    f = _fn(_lib_basic(), "llb_act_rows", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p])
+    _check(f(_ptr(x), _dt(x), x.shape[0], x.stride(0), x.shape[1], ROW_ACTS[act], _ptr(logit),
+             logit.stride(0) if logit is not None else 0, float(scale), _stream()), f"activation of rows ({act})")
+    return x
+
+
+class _StreamUpdateParams(ctypes.Structure):
+    _fields_ = [("cur", c_void_p), ("delta", c_void_p), ("n_part", c_int), ("part_stride", c_longlong), ("delta_scale", c_float),
+                ("write_back", c_int), ("mix", c_void_p), ("n", c_int), ("x0", c_void_p), ("planes", c_void_p),
+                ("plane_stride", c_longlong), ("dst", c_void_p), ("weight", c_void_p), ("out", c_void_p), ("rows", c_void_p),
+                ("H", c_int), ("eps", c_float)]
+
+
+def stream_update(cur: torch.Tensor, delta: Optional[torch.Tensor] = None, delta_scale: float = 1.0, *, mix: Optional[torch.Tensor] = None,
+                  x0: Optional[torch.Tensor] = None, planes: Optional[torch.Tensor] = None, dst: Optional[torch.Tensor] = None,
+                  weight: Optional[torch.Tensor] = None, eps: float = 0.0, out_dtype: Optional[torch.dtype] = None,
+                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One pass over the rows of the float32 stream `cur` [T, H]:
+
+        v = cur + delta_scale * delta            (delta [T, H] or [parts, T, H]; written back to cur unless `rows`)
+        y = sum_j mix[j] X_j                     (with mix, float32 [n]: X_0 = x0, X_1 .. X_{n-2} the planes [n - 2, T, H],
+                                                  X_{n-1} = v; without mix y = v)
+        dst = y                                  (with dst, float32)
+        returns y / sqrt(mean(y^2) + eps) * weight in out_dtype (with weight), else None
+
+    With rows (int32) only those rows are worked on, nothing is written back, and dst / the result have len(rows) rows."""
+    _need_cuda(cur, delta, mix, x0, planes, dst, weight, rows)
+    assert cur.dtype == torch.float32 and cur.is_contiguous() and cur.dim() == 2
+    T, H = cur.shape
+    R = T if rows is None else rows.numel()
+    p = _StreamUpdateParams()
+    p.cur, p.H, p.eps, p.delta_scale = cur.data_ptr(), H, float(eps), float(delta_scale)
+    if delta is not None:
+        assert delta.shape[-2:] == cur.shape and delta.is_contiguous()
+        p.delta, p.n_part, p.part_stride = delta.data_ptr(), (delta.shape[0] if delta.dim() == 3 else 1), (delta.stride(0) if delta.dim() == 3 else 0)
+        p.write_back = int(rows is None)
+    if mix is not None:
+        n = mix.numel()
+        assert mix.dtype == torch.float32 and mix.is_contiguous() and n >= 1
+        p.mix, p.n = mix.data_ptr(), n
+        if n > 1:
+            assert x0 is not None and x0.dtype == torch.float32 and x0.is_contiguous() and x0.shape == cur.shape
+            p.x0 = x0.data_ptr()
+        if n > 2:
+            assert planes is not None and planes.dtype == torch.float32 and planes.shape[0] >= n - 2 and planes.shape[1:] == cur.shape
+            assert planes.stride(1) == H and planes.stride(2) == 1
+            p.planes, p.plane_stride = planes.data_ptr(), planes.stride(0)
+    if dst is not None:
+        assert dst.dtype == torch.float32 and dst.is_contiguous() and dst.shape == (R, H)
+        p.dst = dst.data_ptr()
+    out = None
+    if weight is not None:
+        assert weight.numel() == H and weight.is_contiguous()
+        out = torch.empty((R, H), dtype=out_dtype or torch.float32, device=cur.device)
+        p.weight, p.out = weight.data_ptr(), out.data_ptr()
+    p.rows = _ptr(rows)
+    f = _fn(_lib_basic(), "llb_stream_update", [_StreamUpdateParams, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(p, _dt(delta) if delta is not None else 0, _dt(weight) if weight is not None else 0,
+             DT[out.dtype] if out is not None else 0, R, _stream()), "stream update (scaled add, depth average, norm)")
+    return out
+
+
 def rope_lead_append(proj: torch.Tensor, nh: int, nkvh: int, dk: int, dv: int, rot: int, *, cos=None, sin=None, tok_pos=None,
                      append=None, err=None):
     """In place on packed projections [T, nh dk (+ nkvh dk + nkvh dv)]: rotate the first `rot` dimensions of the query
@@ -621,7 +693,8 @@ class _AttnParams(ctypes.Structure):
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p),
                 ("keep_first", c_int), ("pinned", c_int), ("sink", c_int),
-                ("sink_logits", c_void_p), ("v_in_k", c_int), ("kv_row_stride", c_int)]
+                ("sink_logits", c_void_p), ("v_in_k", c_int), ("kv_row_stride", c_int),
+                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int)]
 
 
 class _MmaAttnParams(ctypes.Structure):
@@ -705,16 +778,25 @@ class AttnExtras:
     """What the plain causal (windowed) softmax attention does not have: values of a width of their own, first keys
     that stay visible behind a window (`keep_first`, held in `pinned` pages ahead of the cache ring), and a
     value-less sink term in the softmax's denominator: of score 0 (`sink`), or of a learned score per query head
-    (`sink_logits`, float32 [heads])."""
+    (`sink_logits`, float32 [heads]); a penalty on distance, `dist_bias` = (r1, r2), float32 [heads] each: the score of
+    query position i and key position j loses r1[h] ln(1 + r2[h] (i - j)); a query temperature, `q_temp` = (coef, every):
+    the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  The last two run on the CUDA-core
+    kernel (both precisions)."""
     value_dim: Optional[int] = None
     keep_first: int = 0
     pinned: int = 0
     sink: bool = False
     sink_logits: Optional[torch.Tensor] = None
+    dist_bias: Optional[tuple] = None
+    q_temp: Optional[tuple] = None
 
     def plain(self, dh: int) -> bool:
         return (self.value_dim in (None, dh) and not self.keep_first and not self.pinned and not self.sink
-                and self.sink_logits is None)
+                and self.sink_logits is None and not self.positional())
+
+    def positional(self) -> bool:
+        """True with an option that makes a score depend on the positions themselves."""
+        return self.dist_bias is not None or self.q_temp is not None
 
 
 def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
@@ -729,6 +811,17 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
         if extras.sink_logits is not None:
             assert extras.sink_logits.dtype == torch.float32 and extras.sink_logits.numel() == nh
             p.sink_logits = extras.sink_logits.data_ptr()
+        if extras.positional():
+            if cls is not None and cls is not _AttnParams:
+                raise KernelError("attention: a distance penalty or a query temperature needs the CUDA-core kernel")
+            if extras.dist_bias is not None:
+                r1, r2 = extras.dist_bias
+                assert r1.dtype == r2.dtype == torch.float32 and r1.numel() == r2.numel() == nh and r1.is_cuda and r2.is_cuda
+                p.dist_r1, p.dist_r2 = r1.data_ptr(), r2.data_ptr()
+            if extras.q_temp is not None:
+                p.q_temp_coef, p.q_temp_every = float(extras.q_temp[0]), int(extras.q_temp[1])
+                if p.q_temp_every <= 0:
+                    raise KernelError("attention: the query temperature's period must be positive")
     p.row_stride = qkv.stride(0)
     p.out = out.data_ptr()
     p.kpool, p.vpool = kpool.data_ptr(), vpool.data_ptr()
@@ -844,13 +937,13 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
     dv = extras.value_dim or dh
     out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
     if (not decode and dv == dh and all_from_cache and prefill_tc_ok(qkv.dtype, dh) and not extras.pinned and scale > 0
-            and extras.sink_logits is None
+            and extras.sink_logits is None and not extras.positional()
             and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0):
         # a cache that keeps every key, head size 64 or 128: the tcgen05 prefill kernel, as for the plain attention
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
                               window, scale, 0, extras.keep_first, extras.sink)
         return out
-    if dv == dh and _mma_ok(qkv, dh):
+    if dv == dh and _mma_ok(qkv, dh) and not extras.positional():
         # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
                          _MmaAttnParams, extras=extras)
@@ -912,28 +1005,36 @@ def moe_tile_rows() -> int:
     return _moe_tile
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, route_scale: float):
+MOE_GATES = {"sigmoid": 0, "softmax_chosen": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, route_scale: float,
+              gate: str = "sigmoid", n_experts: Optional[int] = None, with_logits: bool = False):
     """(int32 [T, top] experts, float32 [T, top] weights): the router's logits x router^T in float32 (a matrix product
-    with float32 accumulation: on the tensor cores for bfloat16 operands, on the CUDA cores in float32), gates
-    sigmoid(logits); the `top` largest of gate + bias are chosen (first maximum first); a weight is gate * route_scale."""
+    with float32 accumulation: on the tensor cores for bfloat16 operands, on the CUDA cores in float32).  gate "sigmoid":
+    gates sigmoid(logits); the `top` largest of gate + bias are chosen (first maximum first); a weight is
+    gate * route_scale.  gate "softmax_chosen": the `top` largest logits (+ bias) are chosen and the weights are the softmax
+    over the chosen logits alone, times route_scale.  n_experts: the router's matrix has further rows after the experts'
+    (other per-token logits that ride on the same product); with_logits also returns all logits [T, rows] (float32)."""
     _need_cuda(x, router, bias)
     T, H = x.shape
-    E = router.shape[0]
-    assert router.shape == (E, H) and router.is_contiguous() and x.stride(1) == 1
+    rows = router.shape[0]
+    E = rows if n_experts is None else int(n_experts)
+    assert router.shape == (rows, H) and E <= rows and router.is_contiguous() and x.stride(1) == 1
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E)
     plan = None
     if T > 256 and _tc_ok(x, router, None):
         # many tokens against a handful of rows: tiles of 64 tokens and the K range cut over a cluster, so that the
         # product runs on more than T / 256 blocks
-        tiles, kblocks = -(-T // 64) * -(-E // 128), -(-H // 64)
+        tiles, kblocks = -(-T // 64) * -(-rows // 128), -(-H // 64)
         splits = max([s for s in (1, 2, 4, 8) if s == 1 or (tiles * s <= 2 * _sm_count(x.device) and s <= kblocks // 2)])
         plan = (64, splits)
     z = linear(x, router, out_dtype=torch.float32, plan=plan)
     idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
-    _check(f(_ptr(z), z.stride(0), _ptr(bias), T, E, top, route_scale, _ptr(idx), _ptr(wgt), _stream()), "router's choice")
-    return idx, wgt
+    f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(bias), T, E, top, route_scale, _ptr(idx), _ptr(wgt), MOE_GATES[gate], _stream()), "router's choice")
+    return (idx, wgt, z) if with_logits else (idx, wgt)
 
 
 class MoePlan:
@@ -960,7 +1061,8 @@ def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: Optional[int] = None)
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, act: Optional[str], out_dtype: torch.dtype) -> torch.Tensor:
     """out[slot] = act(a[row(slot)] w[expert(slot)]^T) for every slot of the plan; w is [E, N, K].  gather: `a` holds the
-    tokens' rows [T, K] and a slot's row is its pair's token; else `a` is [slots, K].  act: None or "relu_squared"."""
+    tokens' rows [T, K] and a slot's row is its pair's token; else `a` is [slots, K].  act: None, "relu_squared" or "gelu"
+    (the erf form)."""
     _need_cuda(a, w)
     E, N, K = w.shape
     assert w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and plan.tile_rows <= moe_tile_rows()
@@ -968,7 +1070,7 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, act:
     f = _fn(_moe_lib(), "llb_moe_gemm", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(plan.pair_of), plan.top, int(gather), _ptr(w), _dt(w), _ptr(out), DT[out_dtype],
-             out.stride(0), _ptr(plan.tiles), plan.max_tiles, _ptr(plan.n_tiles), N, K, {None: 0, "relu_squared": 1}[act],
+             out.stride(0), _ptr(plan.tiles), plan.max_tiles, _ptr(plan.n_tiles), N, K, {None: 0, "relu_squared": 1, "gelu": 2}[act],
              _stream()), "experts' product")
     return out
 
@@ -1001,13 +1103,13 @@ def moe_gather_rows(x: torch.Tensor, plan: MoePlan) -> torch.Tensor:
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, epilogue: str, out: Optional[torch.Tensor] = None,
                 wgt: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """The experts' product on tcgen05 over activations in slot order a [slots, K] (bfloat16), w [E, N, K].
-    epilogue "store" / "relu_squared": returns [slots, N] in out_dtype; "weighted_add": `out` is the float32 stream
+    epilogue "store" / "relu_squared" / "gelu" (erf form): returns [slots, N] in out_dtype; "weighted_add": `out` is the float32 stream
     [T, N] and row token(slot) gets wgt[pair(slot)] * product added (float32 atomics)."""
     _need_cuda(a, w, out, wgt)
     E, N, K = w.shape
     assert w.is_contiguous() and a.stride(1) == 1 and a.shape == (plan.n_pairs, K) and a.dtype == w.dtype == torch.bfloat16
     assert plan.max_tiles and plan.tile_rows in (16, 64, 128)
-    code = {"store": 0, "relu_squared": 1, "weighted_add": 2}[epilogue]
+    code = {"store": 0, "relu_squared": 1, "weighted_add": 2, "gelu": 3}[epilogue]
     if code == 2:
         assert out is not None and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == N and wgt is not None
     else:

@@ -66,7 +66,7 @@ class BuildEnv:
 @dataclass(frozen=True)
 class TensorDecl:
     """A tensor a part wants from the weights file.  kind: "float" or "int".  init: how the
-    random-weights mode fills it ("normal": N(0, 0.02); "one_plus_normal": 1 + N(0, 0.02)).
+    random-weights mode fills it ("normal": N(0, 0.02); "one_plus_normal": 1 + N(0, 0.02); "mean:<m>": m + N(0, 0.02)).
     use: "matrix" for an operand of a matrix product or a table of rows (kept in the model's
     dtype, whatever the file stores, so that it can feed the tensor cores), "vector" for what
     enters 32-bit arithmetic only (a norm's weight, a bias: under a bfloat16 model such a tensor

@@ -1,6 +1,9 @@
 from __future__ import annotations
 
-from .base import Block, register_part
+import torch
+
+from ..config.spec import PartSpec
+from .base import Block, TensorDecl, register_part
 
 
 @register_part("block", "pre_norm_residual")
@@ -15,7 +18,7 @@ class PreNormResidual(Block):
 
     def forward(self, residual, pending, ctx, users):
         from .. import kernels
-        if isinstance(pending, PendingNormed):
+        if isinstance(pending, Deferred):
             pending = settle(residual, pending)
         mixers = iter(users)
         for sub in self.sublayers:
@@ -43,7 +46,7 @@ class ParallelResidual(Block):
 
     def forward(self, residual, pending, ctx, users):
         from .. import kernels
-        if isinstance(pending, PendingNormed):
+        if isinstance(pending, Deferred):
             pending = settle(residual, pending)
         if pending is not None:
             kernels.residual_add(residual, pending)
@@ -97,17 +100,109 @@ class SandwichResidual(Block):
         return residual, pending
 
 
-class PendingNormed:
+@register_part("block", "depth_averaged_residual")
+class DepthAveragedResidual(Block):
+    """x -> x + mult * part(norm(x)) for every sub-layer in turn, and then, as what the next layer (or the output norm)
+    reads, a weighted sum over depth: with X_0 the embedding's output and X_(k+1) the result of the k-th layer of this
+    kind (before any averaging), layer i hands on  sum_{j <= i+1} a_i[j] X_j,  a_i the layer's tensor of i + 2 weights.
+
+    The results are kept for the step in one buffer of planes ([layers + 1, T, H] float32, made by the step's first
+    layer of this kind): layer i works in plane i, which starts as what the layer before handed on and ends as
+    X_(i+1).  Every pass over the stream is one launch (kernels.stream_update): the scaled add of a part's output with
+    the next sub-layer's norm; at a layer's end the scaled add, the sum over depth into the next plane and the next
+    layer's first norm, which the layer leaves pending (PendingDepthSum) for whoever reads the stream next.  A part that
+    can add its scaled output to the stream itself (`scaled_into`) does.  Needs RMS norms.
+
+    params: mult, index (which layer of this kind: 0, 1, ...), layers (how many there are), prefix, tensor (the weights'
+    local name, default "dwa": the file's name is prefix.tensor)."""
+    capturable = True
+
+    def __init__(self, sublayers, env, params=None):
+        super().__init__(sublayers, env, params)
+        p = self.params
+        self.mult, self.index, self.layers = float(p.get("mult", 1.0)), int(p["index"]), int(p["layers"])
+        if not (0 <= self.index < self.layers):
+            raise ValueError(f"layer {self.index} of {self.layers}")
+        self.tensor = str(p.get("tensor", "dwa"))
+        self.spec = PartSpec("depth_averaged_residual", p, prefix=str(p.get("prefix", "")))
+        for sub in self.sublayers:
+            if sub.norm is None or sub.norm.kind != "rms_norm":
+                raise ValueError("every sub-layer of this arrangement sits behind an RMS norm")
+        self.weights = None
+
+    def tensors(self):
+        n = self.index + 2
+        return {self.tensor: TensorDecl((n,), init=f"mean:{1.0 / n}", use="vector")}
+
+    def load(self, tensors):
+        self.weights = tensors[self.tensor].float().contiguous()
+
+    def forward(self, residual, pending, ctx, users):
+        from .. import kernels
+        first = self.sublayers[0].norm
+        if isinstance(pending, PendingDepthSum):
+            planes, x0 = pending.planes, pending.x0
+            h = pending.settle(residual, first)
+        else:
+            # the step's first layer of this kind: what it is handed is X_0; it works on a copy in plane 0
+            if isinstance(pending, Deferred):
+                pending = settle(residual, pending)
+            T, H = residual.shape
+            planes = torch.empty((self.layers + 1, T, H), dtype=torch.float32, device=residual.device)
+            x0 = residual
+            h = kernels.stream_update(x0, pending, 1.0, dst=planes[0], weight=first.weight, eps=first.eps, out_dtype=self.env.dtype)
+            residual = planes[0]
+        mixers = iter(users)
+        delta = None
+        for i, sub in enumerate(self.sublayers):
+            if i > 0:
+                h = kernels.stream_update(residual, delta, self.mult, weight=sub.norm.weight, eps=sub.norm.eps, out_dtype=self.env.dtype)
+            if sub.category == "mixer":
+                delta = sub.part.forward(h, ctx, next(mixers))
+            elif getattr(sub.part, "scaled_into", False) and sub.part.forward_into(h, ctx, residual, scale=self.mult):
+                delta = None
+            else:
+                delta = sub.part.forward(h, ctx)
+        return planes[self.index + 1], PendingDepthSum(residual, delta, self.mult, self.weights, x0, planes)
+
+
+class Deferred:
+    """What a block may leave for whoever reads the stream next (the next block's first norm, or the output norm)."""
+
+
+class PendingNormed(Deferred):
     """A part's output that has not joined the stream yet: it is to be normed by `norm`, scaled by `mult` and added."""
 
     def __init__(self, delta, norm, mult):
         self.delta, self.norm, self.mult = delta, norm, mult
 
 
+class PendingDepthSum(Deferred):
+    """The end of a depth-averaged layer that has not run yet: `cur` (the layer's plane) still lacks mult * delta, and
+    the stream handed on is the weighted sum of x0, the planes before cur's and cur."""
+
+    def __init__(self, cur, delta, mult, weights, x0, planes):
+        self.cur, self.delta, self.mult, self.weights, self.x0, self.planes = cur, delta, mult, weights, x0, planes
+
+    def settle(self, dst, norm=None, rows=None):
+        """The sum into `dst` (the plane the next layer works on); returns norm of it (None without a norm).  With
+        `rows` only those rows of the sum are formed and normed, and dst is not written."""
+        from .. import kernels
+        if norm is not None and norm.kind != "rms_norm":
+            kernels.stream_update(self.cur, self.delta, self.mult, mix=self.weights, x0=self.x0, planes=self.planes, dst=dst)
+            return norm.forward(dst, None, rows=rows)
+        return kernels.stream_update(self.cur, self.delta, self.mult, mix=self.weights, x0=self.x0, planes=self.planes,
+                                     dst=None if rows is not None else dst, rows=rows,
+                                     weight=norm.weight if norm is not None else None,
+                                     eps=norm.eps if norm is not None else 0.0, out_dtype=norm.env.dtype if norm is not None else None)
+
+
 def settle(residual, pending, norm=None, rows=None):
     """Adds whatever the block before left pending to the float32 stream and returns `norm` of the result (None without
     a norm).  With `rows` only those rows are returned (the stream itself is still brought up to date)."""
     from .. import kernels
+    if isinstance(pending, PendingDepthSum):
+        return pending.settle(residual, norm, rows)
     if isinstance(pending, PendingNormed):
         if rows is None:
             try:

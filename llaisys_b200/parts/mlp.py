@@ -51,10 +51,11 @@ class SwiGLUMLP(FeedForward):
 
 @register_part("ffn", "gated_mlp")
 class GatedMLP(FeedForward):
-    """down(act(gate(x)) * up(x)), no biases, with the activation a parameter: "silu", "relu" or "gelu_tanh".  The gate
+    """down(act(gate(x)) * up(x)) with the activation a parameter: "silu", "relu" or "gelu_tanh".  The gate
     and up matrices are kept as one [2I, H] matrix so that one product serves both; the activation and the product of
-    the halves are one pass in float32.  The result is returned in float32 (it may be normed before it joins the
-    stream).  params: hidden_size, intermediate_size, act, names (local tensor names of gate, up, down)."""
+    the halves are one pass in float32.  With `bias` every projection has a bias (tensors named after the matrices with
+    `bias_suffix`, default ".b").  The result is returned in float32 (it may be normed or scaled before it joins the
+    stream).  params: hidden_size, intermediate_size, act, bias, bias_suffix, names (local tensor names of gate, up, down)."""
     capturable = True
 
     def __init__(self, spec, env):
@@ -64,25 +65,35 @@ class GatedMLP(FeedForward):
         if self.act not in kernels.ops.GLU_ACTS:
             raise ValueError(f"unknown activation {self.act!r}; known: {sorted(kernels.ops.GLU_ACTS)}")
         self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **(p.get("names") or {}))
-        self.gate_up = self.down = None
+        self.bias, self.bias_suffix = bool(p.get("bias", False)), str(p.get("bias_suffix", ".b"))
+        self.gate_up = self.down = self.b_gate_up = self.b_down = None
 
     def tensors(self):
         n = self.names
-        return {n["gate"]: TensorDecl((self.inter, self.hidden)), n["up"]: TensorDecl((self.inter, self.hidden)),
-                n["down"]: TensorDecl((self.hidden, self.inter))}
+        t = {n["gate"]: TensorDecl((self.inter, self.hidden)), n["up"]: TensorDecl((self.inter, self.hidden)),
+             n["down"]: TensorDecl((self.hidden, self.inter))}
+        if self.bias:
+            t.update({n["gate"] + self.bias_suffix: TensorDecl((self.inter,), use="vector"),
+                      n["up"] + self.bias_suffix: TensorDecl((self.inter,), use="vector"),
+                      n["down"] + self.bias_suffix: TensorDecl((self.hidden,), use="vector")})
+        return t
 
     def load(self, tensors):
         g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         dt = torch.promote_types(g.dtype, u.dtype)
         self.gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.down = tensors[self.names["down"]].contiguous()
+        if self.bias:
+            b = self.bias_suffix
+            self.b_gate_up = torch.cat([tensors[self.names["gate"] + b].float(), tensors[self.names["up"] + b].float()]).contiguous()
+            self.b_down = tensors[self.names["down"] + b].float().contiguous()
 
     def forward(self, x, ctx):
-        if self.act == "silu":
+        if self.act == "silu" and not self.bias:
             act = kernels.linear_swiglu(x, self.gate_up)
         else:
-            act = kernels.glu(kernels.linear(x, self.gate_up), self.act)
-        return kernels.linear(act, self.down, out_dtype=delta_dtype(act))
+            act = kernels.glu(kernels.linear(x, self.gate_up, self.b_gate_up), self.act)
+        return kernels.linear(act, self.down, self.b_down, out_dtype=delta_dtype(act))
 
 
 def delta_dtype(x):

@@ -18,18 +18,29 @@ class RoutedExperts(FeedForward):
       expert    Wd act(Wu h), no biases; act = max(., 0)^2 ("relu_squared")
       output    sum over the chosen experts of weight * expert(h), plus shared(h)
 
+    Variants.  `gate` "softmax_chosen": the `top` experts with the largest logits Wr h (+ bias) are chosen and their
+    weights are the softmax over the chosen logits alone (times route_scale).  `act` "gelu": an expert is
+    Wd gelu(Wu h) with the erf form of gelu.  `shared_gate`: the shared expert's output is multiplied by
+    sigmoid(w_sg . h), one number per token (tensor `shared_gate`, [1, hidden]); its logit rides on the router's
+    product as one more row of the matrix.
+
     The experts' matrices are kept stacked ([E, ff, H] and [E, H, ff]).  A step's (token, choice) pairs are grouped by
     expert on the device (kernels.moe_plan) and the two products run over those groups: in bfloat16 on tcgen05, the
     second one ending in the weighted add into the float32 residual stream (float32 atomics, arrival order); in float32
     (and for widths the tensor-core kernel does not take) on the CUDA cores with the weighted sum added in a fixed
     order.  Nothing is read back to the host, so a step can be captured.
 
-    params: hidden_size, experts, top, expert_ff, route_scale, act, shared_ff (None: no shared expert), use_bias, names
-    (local tensor names: router, bias, expert_up, expert_down with {e} for the expert's index, shared_up, shared_down).
+    forward_into(..., scale=c) adds c times the part's output (the weights and the shared expert's activations carry the
+    factor), for arrangements whose parts join the stream scaled.
+
+    params: hidden_size, experts, top, expert_ff, route_scale, gate, act, shared_ff (None: no shared expert), shared_gate,
+    use_bias, names (local tensor names: router, bias, expert_up, expert_down with {e} for the expert's index, shared_up,
+    shared_down, shared_gate).
     """
     capturable = True
+    scaled_into = True
     NAMES = {"router": "router", "bias": "correction", "expert_up": "e{e}.up", "expert_down": "e{e}.down",
-             "shared_up": "shared.up", "shared_down": "shared.down"}
+             "shared_up": "shared.up", "shared_down": "shared.down", "shared_gate": "shared.sg"}
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -38,12 +49,16 @@ class RoutedExperts(FeedForward):
         self.ff = int(p["expert_ff"])
         self.route_scale = float(p.get("route_scale", 1.0))
         self.act = str(p.get("act", "relu_squared"))
-        if self.act != "relu_squared":
-            raise ValueError(f"expert activation {self.act!r} is not built (relu_squared)")
+        if self.act not in ("relu_squared", "gelu"):
+            raise ValueError(f"expert activation {self.act!r} is not built (relu_squared, gelu)")
+        self.gate = str(p.get("gate", "sigmoid"))
+        if self.gate not in kernels.ops.MOE_GATES:
+            raise ValueError(f"unknown router gate {self.gate!r}; known: {sorted(kernels.ops.MOE_GATES)}")
         if not (1 <= self.top <= self.n_experts):
             raise ValueError(f"a token cannot use {self.top} of {self.n_experts} experts")
         self.shared_ff = int(p["shared_ff"]) if p.get("shared_ff") else None
         self.use_bias = bool(p.get("use_bias", True))
+        self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_ff is not None
         self.names = dict(self.NAMES, **(p.get("names") or {}))
         self.router = self.bias = self.up = self.down = self.shared_up = self.shared_down = None
 
@@ -58,11 +73,18 @@ class RoutedExperts(FeedForward):
         if self.shared_ff:
             t[n["shared_up"]] = TensorDecl((self.shared_ff, self.hidden))
             t[n["shared_down"]] = TensorDecl((self.hidden, self.shared_ff))
+        if self.shared_gate:
+            t[n["shared_gate"]] = TensorDecl((1, self.hidden))
         return t
 
     def load(self, tensors):
         n = self.names
         self.router = tensors[n["router"]].contiguous()
+        if self.shared_gate:
+            # the shared expert's gate logit is one more row of the router's product
+            sg = tensors[n["shared_gate"]].reshape(1, self.hidden)
+            dt = torch.promote_types(self.router.dtype, sg.dtype)
+            self.router = torch.cat([self.router.to(dt), sg.to(dt)], dim=0).contiguous()
         self.bias = tensors[n["bias"]].to(torch.float32).contiguous() if self.use_bias else None
         self.up = torch.stack([tensors[n["expert_up"].format(e=e)] for e in range(self.n_experts)]).contiguous()
         self.down = torch.stack([tensors[n["expert_down"].format(e=e)] for e in range(self.n_experts)]).contiguous()
@@ -74,8 +96,9 @@ class RoutedExperts(FeedForward):
         self.forward_into(x, ctx, out)
         return out
 
-    def forward_into(self, x, ctx, residual):
-        idx, wgt = kernels.moe_route(x, self.router, self.bias, self.top, self.route_scale)
+    def forward_into(self, x, ctx, residual, scale: float = 1.0):
+        idx, wgt, z = kernels.moe_route(x, self.router, self.bias, self.top, self.route_scale * scale, gate=self.gate,
+                                        n_experts=self.n_experts, with_logits=True)
         tc = kernels.moe_tc_ok(x, self.up, self.down) and residual.stride(1) == 1
         plan = kernels.moe_plan(idx, self.n_experts, kernels.moe_tc_tile_rows(idx.numel(), self.n_experts) if tc else None)
         if tc:
@@ -88,7 +111,11 @@ class RoutedExperts(FeedForward):
             y = kernels.moe_gemm(act, self.down, plan, gather=False, act=None, out_dtype=torch.float32)
             kernels.moe_combine(residual, y, plan, wgt)
         if self.shared_ff:
-            a = kernels.relu_squared_(kernels.linear(x, self.shared_up))
+            a = kernels.linear(x, self.shared_up)
+            if self.shared_gate or scale != 1.0 or self.act != "relu_squared":
+                kernels.act_rows_(a, self.act, z[:, self.n_experts] if self.shared_gate else None, scale)
+            else:
+                kernels.relu_squared_(a)
             if kernels.linear_into_ok(a, self.shared_down, None, residual):
                 kernels.linear_into(a, self.shared_down, None, residual)
             else:

@@ -85,8 +85,10 @@ class RotaryLeading(PositionEncoding):
     pair (a, b) at position p becomes (a cos phi - b sin phi, b cos phi + a sin phi), phi = p * base^(-2i/dims); the
     dimensions from `dims` on pass unchanged.  dims = head_dim is the half-split rotation of whole heads; dims = 0
     encodes nothing.  Tables [positions, dims/2] are built in float64 on the host and kept in float32, sized once by
-    prepare().  params: head_dim, dims, base."""
+    prepare().  Mixers that rotate in their own kernels take the tables through pair_tables(); `pair_layout` tells them
+    which dimensions pair up.  params: head_dim, dims, base."""
     capturable = True
+    pair_layout = "halves"
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -115,6 +117,11 @@ class RotaryLeading(PositionEncoding):
 
     def rotation_tables(self, positions: int):
         return self.leading_tables(positions) if self.dims == self.head_dim else None
+
+    def pair_tables(self, positions: int):
+        """(cos, sin, dims), the tables float32 [rows >= positions, dims / 2]; None when nothing is rotated."""
+        t = self.leading_tables(positions)
+        return None if t is None else (t[0], t[1], self.dims)
 
     def apply(self, qkv, num_heads, num_kv_heads, ctx):
         t = self.leading_tables(ctx.max_position + 1)
@@ -154,6 +161,7 @@ class RotaryInterleaved(PositionEncoding):
     [positions, dims / 2] of cos and sin (magnitude included), built in float64 on the host and sized once by
     prepare(); the mixers' kernels apply them.  params: width, dims, base, yarn (dict or None)."""
     capturable = True
+    pair_layout = "neighbours"
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

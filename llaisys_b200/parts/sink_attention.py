@@ -9,13 +9,17 @@ from .base import KVNeed, Mixer, TensorDecl, build_part, register_part
 
 @register_part("mixer", "windowed_sink_attention")
 class WindowedSinkAttention(Mixer):
-    """Causal grouped-query attention over the paged cache with four options the plain one does not have:
+    """Causal grouped-query attention over the paged cache with six options the plain one does not have:
 
       * keys and queries of `key_dim` elements, values (and the heads' outputs) of `value_dim`;
       * a window that keeps a sequence's first keys: the query at position i sees key j <= i when i - j < window or
         j < keep_first (the kept keys stay at their true positions);
       * a sink: the softmax's denominator has one more term e^0 that carries no value, so the weights are
         e^{s_j} / (1 + sum e^{s_j}) and may sum to less than one;
+      * a penalty on distance (`distance_bias`): the score of query position i and key position j loses
+        r1[h] ln(1 + r2[h] (i - j)), with two numbers per query head (tensors `r1`, `r2`, [num_heads]);
+      * a query temperature (`q_temp` = {coef, every}): the query at position p is multiplied by
+        1 + coef ln(floor((p + 1) / every) + 1), i.e. queries sharpen as the sequence grows, in steps of `every`;
       * a layer without key and value projections (`own_kv` false) that reads the rotated keys and the values another
         layer stored in the cache (the run order's `cache_of`), with queries, window and everything else its own.
 
@@ -30,7 +34,8 @@ class WindowedSinkAttention(Mixer):
     otherwise (and in decode) keys and values are appended first and attention reads the cache alone.
 
     params: hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale, window, keep_first, sink, own_kv,
-    cache_window, position (PartSpec), names (local tensor names of q, k, v, o; default those letters).
+    cache_window, position (PartSpec or None: no rotation), distance_bias, q_temp, names (local tensor names of q, k, v, o,
+    r1, r2; default those).
     """
 
     def __init__(self, spec, env):
@@ -56,8 +61,14 @@ class WindowedSinkAttention(Mixer):
         if self.position is not None and not hasattr(self.position, "leading_tables"):
             raise ValueError("this mixer takes a position encoding that rotates a head's leading dimensions")
         self.rot = self.position.dims if self.position is not None else 0
-        self.names = dict({"q": "q", "k": "k", "v": "v", "o": "o"}, **(p.get("names") or {}))
-        self.w_in = self.w_o = None
+        self.names = dict({"q": "q", "k": "k", "v": "v", "o": "o", "r1": "r1", "r2": "r2"}, **(p.get("names") or {}))
+        self.distance_bias = bool(p.get("distance_bias", False))
+        self.q_temp = None
+        if p.get("q_temp"):
+            self.q_temp = (float(p["q_temp"]["coef"]), int(p["q_temp"]["every"]))
+            if self.q_temp[1] <= 0:
+                raise ValueError(f"the query temperature's period must be positive, got {self.q_temp[1]}")
+        self.w_in = self.w_o = self.r1 = self.r2 = None
 
     capturable = True
 
@@ -74,6 +85,9 @@ class WindowedSinkAttention(Mixer):
         if self.own_kv:
             t[n["k"]] = TensorDecl((self.nkvh * self.dk, self.hidden))
             t[n["v"]] = TensorDecl((self.nkvh * self.dv, self.hidden))
+        if self.distance_bias:
+            t[n["r1"]] = TensorDecl((self.nh,), init="one_plus_normal", use="vector")
+            t[n["r2"]] = TensorDecl((self.nh,), init="one_plus_normal", use="vector")
         return t
 
     def load(self, tensors):
@@ -84,6 +98,8 @@ class WindowedSinkAttention(Mixer):
             dt = torch.promote_types(dt, t.dtype)
         self.w_in = torch.cat([t.to(dt) for t in ts], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
+        if self.distance_bias:
+            self.r1, self.r2 = tensors[n["r1"]].float().contiguous(), tensors[n["r2"]].float().contiguous()
 
     def forward(self, x, ctx, call):
         return kernels.linear(self._attend(x, ctx, call), self.w_o)
@@ -117,7 +133,8 @@ class WindowedSinkAttention(Mixer):
         if kv.writable:
             append = dict(tok_seq=ctx.tok_seq, seq_start=ctx.seq_start, seq_len_before=ctx.seq_len_before, kpool=kv.k,
                           vpool=kv.v, page_table=kv.page_table, ring=kv.ring, pinned=kv.pinned)
-        extras = kernels.AttnExtras(value_dim=self.dv, keep_first=self.keep_first, pinned=kv.pinned, sink=self.sink)
+        extras = kernels.AttnExtras(value_dim=self.dv, keep_first=self.keep_first, pinned=kv.pinned, sink=self.sink,
+                                    dist_bias=(self.r1, self.r2) if self.distance_bias else None, q_temp=self.q_temp)
         common = (proj, self.nh, self.nkvh, self.dk, kv.k, kv.v, kv.page_table, kv.ring, ctx.seq_start, ctx.seq_len_before,
                   ctx.n_seqs)
         ring_cache = kv.writable and self.cache_window is not None

@@ -96,7 +96,8 @@ class RandomSource:
         if d.kind == "int":
             return torch.zeros(d.shape, dtype=torch.int32, device=self.device)
         key = tensor_key(self.seed, name)
-        mean = 1.0 if d.init == "one_plus_normal" else 0.0
+        # "normal": N(0, std); "one_plus_normal": 1 + N(0, std); "mean:<m>": m + N(0, std)
+        mean = 1.0 if d.init == "one_plus_normal" else float(d.init[5:]) if d.init.startswith("mean:") else 0.0
         n = 1
         for s in d.shape:
             n *= s
