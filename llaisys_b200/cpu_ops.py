@@ -95,13 +95,14 @@ def route_top(logits: np.ndarray, bias, top: int, scale: float):
 
 
 def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=None, keep_first: int = 0,
-                   sink: bool = False, sink_logits=None) -> np.ndarray:
+                   sink: bool = False, sink_logits=None, dist_bias=None) -> np.ndarray:
     """Causal grouped-query attention of q [qlen, nh, d] over k [kvlen, nkvh, d], v [kvlen, nkvh, dv], the queries being
     the last qlen of the kvlen positions: query i sees keys t <= kvlen - qlen + i; head h reads kv head
     h // (nh / nkvh); softmax with the maximum subtracted (src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112).
     Not in that project: window (a query at position p sees only the keys p - window < t <= p), keep_first (the keys
     t < keep_first stay visible behind the window), sink (one more term e^0 in the denominator, without a value) and
-    sink_logits [nh] (that term is e^sink_logits[h] instead)."""
+    sink_logits [nh] (that term is e^sink_logits[h] instead), dist_bias = (r1 [nh], r2 [nh]) (the score of query position
+    p and key position t loses r1[h] ln(1 + r2[h] (p - t)))."""
     qlen, nh, d = q.shape
     kvlen, nkvh, dv = v.shape
     group = nh // nkvh
@@ -114,6 +115,9 @@ def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, wi
         visible &= (t[None, :] > cur - window) | (t[None, :] < keep_first)
     for h in range(nh):
         s = (q[:, h, :] @ k[:, h // group, :].T) * np.float32(scale)
+        if dist_bias is not None:
+            dist = np.maximum(cur - t[None, :], 0).astype(np.float32)
+            s = s - np.float32(dist_bias[0][h]) * np.log1p(np.float32(dist_bias[1][h]) * dist)
         s = np.where(visible, s, -np.inf)
         m = s.max(axis=-1, keepdims=True)
         s0 = np.float32(sink_logits[h]) if sink_logits is not None else np.float32(0)
@@ -183,3 +187,44 @@ def gated_linear_recurrence(q: np.ndarray, k: np.ndarray, v: np.ndarray, z: np.n
         state += k[t][:, :, None] * v[t][:, None, :]
         out[t] = np.einsum("hkv,hk->hv", state, q[t])
     return out
+
+
+def query_temperature(pos_ids: np.ndarray, coef: float, every: int) -> np.ndarray:
+    """1 + coef ln(floor((p + 1) / every) + 1) per position (not in xsmccc/llaisys)."""
+    p = np.asarray(pos_ids, dtype=np.int64)
+    return (1.0 + float(coef) * np.log(((p + 1) // int(every)) + 1.0)).astype(np.float32)
+
+
+def min_gru(a: np.ndarray, u: np.ndarray, state: np.ndarray) -> np.ndarray:
+    """S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, z = sigmoid(a), c = u + 1/2 where u >= 0 and sigmoid(u) below;
+    a, u [seq, width], state [width] (updated in place).  Returns S [seq, width] (not in xsmccc/llaisys)."""
+    a, u = a.astype(np.float32), u.astype(np.float32)
+    z = np.float32(1) / (np.float32(1) + np.exp(-a))
+    c = np.where(u >= 0, u + np.float32(0.5), np.float32(1) / (np.float32(1) + np.exp(-np.minimum(u, np.float32(0)))))
+    out = np.zeros(a.shape, dtype=np.float32)
+    for t in range(a.shape[0]):
+        state += z[t] * (c[t] - state)
+        out[t] = state
+    return out
+
+
+def gelu(x: np.ndarray) -> np.ndarray:
+    """x Phi(x) with the error function (not in xsmccc/llaisys)."""
+    import math
+    x = x.astype(np.float32)
+    return (np.float32(0.5) * x * (np.float32(1) + np.vectorize(math.erf, otypes=[np.float64])(x / math.sqrt(2.0)))).astype(np.float32)
+
+
+def sigmoid(x: np.ndarray) -> np.ndarray:
+    return np.float32(1) / (np.float32(1) + np.exp(-x.astype(np.float32)))
+
+
+def route_top_softmax(logits: np.ndarray, bias, top: int, scale: float):
+    """(experts [T, top], weights [T, top]): the `top` largest of logits + bias, the first maximum first; weights the
+    softmax over the chosen logits alone, times scale (not in xsmccc/llaisys)."""
+    z = logits.astype(np.float32)
+    choice = z + (bias.astype(np.float32) if bias is not None else np.float32(0))
+    idx = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    zc = np.take_along_axis(z, idx, axis=-1)
+    e = np.exp(zc - zc.max(axis=-1, keepdims=True))
+    return idx, (e / e.sum(axis=-1, keepdims=True)) * np.float32(scale)

@@ -19,9 +19,9 @@ from .. import cpu_ops
 from ..config.spec import ModelSpec, PartSpec
 
 _KNOWN = {"embedding": {"token_embedding", "scaled_pair_embedding"}, "norm": {"rms_norm"},
-          "mixer": {"gqa_attention", "windowed_sink_attention", "gated_linear_attention", "latent_attention"},
+          "mixer": {"gqa_attention", "windowed_sink_attention", "gated_linear_attention", "latent_attention", "min_gru"},
           "ffn": {"swiglu_mlp", "routed_experts", "gated_mlp"},
-          "block": {"pre_norm_residual", "parallel_residual", "sandwich_residual"}, "head": {"lm_head"},
+          "block": {"pre_norm_residual", "parallel_residual", "sandwich_residual", "depth_averaged_residual"}, "head": {"lm_head"},
           "position": {"rope_half_split", "rope_leading", "rope_interleaved"}}
 
 
@@ -84,19 +84,38 @@ class CpuModel:
         g = cpu_ops.linear(x, w("g"))
         return cpu_ops.linear(o * (g / (np.float32(1) + np.exp(-g))), w("o"))
 
+    def _min_gru(self, p: PartSpec, x, store: dict, key):
+        a = p.params
+        n = dict({"z": "z", "z_bias": "z.b", "x": "x", "x_bias": "x.b", "g": "g", "o": "o"}, **(a.get("names") or {}))
+        w = lambda k: self.w[p.tensor_name(n[k])]
+        if key not in store:
+            store[key] = np.zeros(a["width"], dtype=np.float32)
+        S = cpu_ops.min_gru(cpu_ops.linear(x, w("z"), w("z_bias")), cpu_ops.linear(x, w("x"), w("x_bias")), store[key])
+        g = cpu_ops.linear(x, w("g"))
+        return cpu_ops.linear(S * (g * cpu_ops.sigmoid(g)), w("o"))
+
     def _latent(self, p: PartSpec, x, positions, store: dict, key, owner):
         """The heads' keys and values are made from the cached latents here (the engine carries the queries into the
         latent space instead)."""
         a = p.params
         H, dn, dr, dv, r = a["num_heads"], a["nope_dim"], a["rope_dim"], a["value_dim"], a["kv_rank"]
-        n = dict({"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+        n = dict({"q": "q", "dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
                   "sink": "sink", "g": "g", "o": "o"}, **(a.get("names") or {}))
         w = lambda k: self.w[p.tensor_name(n[k])]
-        pos = a["position"].params
-        rot = lambda t: cpu_ops.rope_pairs(t, positions, pos["dims"], pos["base"], pos.get("yarn"))
+        if a.get("position") is None:
+            rot = lambda t: t.astype(np.float32)
+        elif a["position"].kind == "rope_leading":                # pairs (i, i + dims/2)
+            pos = a["position"].params
+            rot = lambda t: cpu_ops.rope_leading(t, positions, pos["dims"], pos["base"])
+        else:
+            pos = a["position"].params
+            rot = lambda t: cpu_ops.rope_pairs(t, positions, pos["dims"], pos["base"], pos.get("yarn"))
         T = x.shape[0]
-        cq = cpu_ops.rms_norm(cpu_ops.linear(x, w("dq")), w("dq_norm"), a["eps"])
-        q = cpu_ops.linear(cq, w("uq")).reshape(T, H, dn + dr)
+        if a.get("q_rank"):
+            cq = cpu_ops.rms_norm(cpu_ops.linear(x, w("dq")), w("dq_norm"), a["eps"])
+            q = cpu_ops.linear(cq, w("uq")).reshape(T, H, dn + dr)
+        else:                                                     # no query latent
+            q = cpu_ops.linear(x, w("q")).reshape(T, H, dn + dr)
         q = np.concatenate([q[:, :, :dn], rot(q[:, :, dn:])], axis=-1)
         if owner is None:
             d = cpu_ops.linear(x, w("dkv"))
@@ -110,21 +129,26 @@ class CpuModel:
         k = np.concatenate([cpu_ops.linear(cs, w("uk")).reshape(L, H, dn), np.broadcast_to(krs[:, None, :], (L, H, dr))], axis=-1)
         v = cpu_ops.linear(cs, w("uv")).reshape(L, H, dv)
         o = cpu_ops.self_attention(q, k, v, a["scale"], a.get("window"), sink_logits=w("sink") if a.get("sink") else None)
-        if a.get("head_gate"):
-            g = cpu_ops.linear(x, w("g"))
-            o = o * (np.float32(1) / (np.float32(1) + np.exp(-g)))[:, :, None]
+        gate = a.get("gate") or ("head" if a.get("head_gate") else None)
+        if gate is not None:
+            g = cpu_ops.sigmoid(cpu_ops.linear(x, w("g")))
+            o = o * (g[:, :, None] if gate == "head" else g.reshape(T, H, dv))
         return cpu_ops.linear(o.reshape(T, H * dv), w("o"))
 
     def _gated_mlp(self, p: PartSpec, x):
         n = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **(p.params.get("names") or {}))
-        g, u = cpu_ops.linear(x, self.w[p.tensor_name(n["gate"])]), cpu_ops.linear(x, self.w[p.tensor_name(n["up"])])
-        return cpu_ops.linear(cpu_ops.glu(g, u, p.params.get("act", "silu")), self.w[p.tensor_name(n["down"])])
+        sfx = p.params.get("bias_suffix", ".b")
+        b = (lambda k: self.w[p.tensor_name(n[k] + sfx)]) if p.params.get("bias") else (lambda k: None)
+        g, u = cpu_ops.linear(x, self.w[p.tensor_name(n["gate"])], b("gate")), cpu_ops.linear(x, self.w[p.tensor_name(n["up"])], b("up"))
+        return cpu_ops.linear(cpu_ops.glu(g, u, p.params.get("act", "silu")), self.w[p.tensor_name(n["down"])], b("down"))
 
     def _part(self, sub, h, positions, store, m, owner):
         """One part's output for normed input h."""
         kind = sub.part.kind
         if kind == "gated_linear_attention":
             return self._gla(sub.part, h, store, m)
+        if kind == "min_gru":
+            return self._min_gru(sub.part, h, store, m)
         if kind == "latent_attention":
             return self._latent(sub.part, h, positions, store, m, owner)
         if kind == "windowed_sink_attention":
@@ -157,11 +181,14 @@ class CpuModel:
     def _sink_attention(self, p: PartSpec, x, positions, store: dict, key, owner):
         a = p.params
         nh, nkvh, dk, dv = a["num_heads"], a["num_kv_heads"], a["key_dim"], a["value_dim"]
-        n = dict({"q": "q", "k": "k", "v": "v", "o": "o"}, **(a.get("names") or {}))
+        n = dict({"q": "q", "k": "k", "v": "v", "o": "o", "r1": "r1", "r2": "r2"}, **(a.get("names") or {}))
         T = x.shape[0]
         pos = a.get("position")
         rot = (lambda t: cpu_ops.rope_leading(t, positions, pos.params["dims"], pos.params["base"])) if pos is not None else (lambda t: t)
         q = rot(cpu_ops.linear(x, self.w[p.tensor_name(n["q"])]).reshape(T, nh, dk))
+        if a.get("q_temp"):
+            q = q * cpu_ops.query_temperature(positions, a["q_temp"]["coef"], a["q_temp"]["every"])[:, None, None]
+        bias = (self.w[p.tensor_name(n["r1"])], self.w[p.tensor_name(n["r2"])]) if a.get("distance_bias") else None
         if owner is None:
             k = rot(cpu_ops.linear(x, self.w[p.tensor_name(n["k"])]).reshape(T, nkvh, dk))
             v = cpu_ops.linear(x, self.w[p.tensor_name(n["v"])]).reshape(T, nkvh, dv)
@@ -170,24 +197,28 @@ class CpuModel:
             ks, vs = store[key]
         else:
             ks, vs = owner[key]
-        o = cpu_ops.self_attention(q, ks, vs, a["scale"], a.get("window"), a.get("keep_first", 0), bool(a.get("sink")))
+        o = cpu_ops.self_attention(q, ks, vs, a["scale"], a.get("window"), a.get("keep_first", 0), bool(a.get("sink")), dist_bias=bias)
         return cpu_ops.linear(o.reshape(T, nh * dv), self.w[p.tensor_name(n["o"])])
 
     def _routed(self, p: PartSpec, x):
         a = p.params
         n = {"router": "router", "bias": "correction", "expert_up": "e{e}.up", "expert_down": "e{e}.down",
-             "shared_up": "shared.up", "shared_down": "shared.down", **(a.get("names") or {})}
+             "shared_up": "shared.up", "shared_down": "shared.down", "shared_gate": "shared.sg", **(a.get("names") or {})}
         bias = self.w[p.tensor_name(n["bias"])] if a.get("use_bias", True) else None
-        idx, wgt = cpu_ops.route_top(cpu_ops.linear(x, self.w[p.tensor_name(n["router"])]), bias, a["top"], a.get("route_scale", 1.0))
+        top_of = cpu_ops.route_top_softmax if a.get("gate") == "softmax_chosen" else cpu_ops.route_top
+        idx, wgt = top_of(cpu_ops.linear(x, self.w[p.tensor_name(n["router"])]), bias, a["top"], a.get("route_scale", 1.0))
+        act = cpu_ops.gelu if a.get("act") == "gelu" else cpu_ops.relu_squared
         out = np.zeros((x.shape[0], a["hidden_size"]), dtype=np.float32)
         for t in range(x.shape[0]):
             for e, wt in zip(idx[t], wgt[t]):
                 up = self.w[p.tensor_name(n["expert_up"].format(e=int(e)))]
                 down = self.w[p.tensor_name(n["expert_down"].format(e=int(e)))]
-                out[t] += wt * cpu_ops.linear(cpu_ops.relu_squared(cpu_ops.linear(x[t:t + 1], up)), down)[0]
+                out[t] += wt * cpu_ops.linear(act(cpu_ops.linear(x[t:t + 1], up)), down)[0]
         if a.get("shared_ff"):
-            out = cpu_ops.add(out, cpu_ops.linear(cpu_ops.relu_squared(cpu_ops.linear(x, self.w[p.tensor_name(n["shared_up"])])),
-                                                  self.w[p.tensor_name(n["shared_down"])]))
+            shared = cpu_ops.linear(act(cpu_ops.linear(x, self.w[p.tensor_name(n["shared_up"])])), self.w[p.tensor_name(n["shared_down"])])
+            if a.get("shared_gate"):
+                shared = shared * cpu_ops.sigmoid(cpu_ops.linear(x, self.w[p.tensor_name(n["shared_gate"])].reshape(1, -1)))
+            out = cpu_ops.add(out, shared)
         return out
 
     def _attention(self, p: PartSpec, x, positions, store: dict, key, owner):
@@ -221,6 +252,7 @@ class CpuModel:
         """Feeds the next tokens of the sequence; returns float32 logits [len(tokens), vocab]."""
         positions = np.arange(self.length, self.length + len(tokens))
         x = self._embed(tokens)
+        results = [x]                                      # depth-averaged layers: the embedding's output and every layer's result
         for c, call in enumerate(self.spec.order):
             owner = self.cache[call.cache_of] if call.cache_of is not None else None
             m = 0
@@ -235,7 +267,13 @@ class CpuModel:
                     m += 1
                 if layer.block == "sandwich_residual":       # the part's output is normed and scaled on its way into the stream
                     y = self._norm(sub.post_norm, y) * np.float32(layer.params.get("mult", 1.0))
+                elif layer.block == "depth_averaged_residual":
+                    y = y * np.float32(layer.params.get("mult", 1.0))
                 x = cpu_ops.add(y, x)
+            if layer.block == "depth_averaged_residual":     # what goes on is a weighted sum of all results so far
+                results.append(x)
+                a = self.w[f"{layer.params['prefix']}.{layer.params.get('tensor', 'dwa')}"].astype(np.float32)
+                x = sum(a[j] * r for j, r in enumerate(results))
         self.length += len(tokens)
         x = self._norm(self.spec.final_norm, x)
         head = self.spec.head
