@@ -555,12 +555,40 @@ def nubedra_configs(size: str, layers: int):
     return nb, qw
 
 
-DESIGNS = {"vumezen": (DESIGN_SIZES, design_configs), "nubedra": (NUBEDRA_SIZES, nubedra_configs)}
+def zedirax_configs(size: str, layers: int):
+    """(Zedirax config, Nubedra config) of one size: the same width, latent-attention sizes and dense feed-forward as the
+    Nubedra model of that size; the minGRU as many channels as the stream is wide (its four matrices then hold what the
+    gated linear attention's projections hold); the attention with a distance penalty at the heads and head size of the
+    Qwen2 model of that size; routed experts as the Vumezen model of that size has them.  Layers in turn: minGRU with a
+    dense feed-forward, latent attention with routed experts, attention with a dense feed-forward, minGRU with routed
+    experts."""
+    D, H, dn, dr, dv, _, kvr, _, ff, _, _, _, G = NUBEDRA_SIZES[size]
+    _, _, _, _, _, _, _, E, top, eff, sff = DESIGN_SIZES[size]
+    vocab = 32768
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": eff}, "shared": {"ff": sff}}
+    kinds = [
+        {"type": "mingru", "mixer": {"width": D}, "mlp": dense},
+        {"type": "latent_attention", "mlp": moe,
+         "mixer": {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": kvr, "scale": (dn + dr) ** -0.5,
+                   "rot": {"dims": dr, "base": 1000000.0}}},
+        {"type": "attention", "mlp": dense,
+         "mixer": {"heads": H, "kv_heads": G, "dim": dn + dr, "vdim": dn + dr, "scale": (dn + dr) ** -0.5,
+                   "q_temp": {"coef": 0.3, "every": 128}}},
+        {"type": "mingru", "mixer": {"width": D}, "mlp": moe},
+    ]
+    zx = {"architecture": "Zedirax", "vocab": vocab, "width": D, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+          "layers": [kinds[i % 4] for i in range(layers)]}
+    return zx, nubedra_configs(size, layers)[0]
+
+
+DESIGNS = {"vumezen": (DESIGN_SIZES, design_configs, "qwen2"), "nubedra": (NUBEDRA_SIZES, nubedra_configs, "qwen2"),
+           "zedirax": (NUBEDRA_SIZES, zedirax_configs, "nubedra")}
 
 
 def design_run(args) -> int:
     """Prefill (one step over --tokens tokens) and decode (--batch sequences that hold --tokens tokens each) of the
-    chosen design and of the Qwen2 dense decoder at equal layer sizes: time per step, tokens a second, and each kernel's
+    chosen design and of the model beside it (the Qwen2 dense decoder; for zedirax the Nubedra design) at equal layer sizes: time per step, tokens a second, and each kernel's
     share of a step (torch.profiler).  One JSON line per model and phase.  Inputs: the weights of either model are
     larger than L2, and nothing is flushed between steps."""
     import collections
@@ -580,9 +608,9 @@ def design_run(args) -> int:
     torch.cuda.set_device(dev)
     layers = args.layers or 8
     T, B = args.tokens, max(1, args.batch)
-    sizes, configs = DESIGNS[args.design]
+    sizes, configs, beside = DESIGNS[args.design]
     for size in (args.size.split(",") if args.size else sorted(sizes)):
-        for name, cfg_dict in zip((args.design, "qwen2"), configs(size, layers)):
+        for name, cfg_dict in zip((args.design, beside), configs(size, layers)):
             cfg = config_from_dict(cfg_dict)
             model = DecoderModel(cfg.to_spec(), BuildEnv(torch.bfloat16, dev))
             load_weights(model, RandomSource(model.expected_tensors(), seed=0, dtype=torch.bfloat16, device=dev))
@@ -795,8 +823,9 @@ def main() -> int:
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
-                    help="measure this design beside the Qwen2 dense decoder at equal layer sizes (prefill of --tokens tokens, "
-                         "decode at --batch) instead of the benchmark; --size picks among the sizes (default: all)")
+                    help="measure this design beside the Qwen2 dense decoder (zedirax: beside the Nubedra design) at equal layer sizes "
+                         "(prefill of --tokens tokens, decode at --batch) instead of the benchmark; --size picks among the sizes "
+                         "(default: all)")
     ap.add_argument("--size", default=None, help="with --design: comma-separated sizes of " + ", ".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
     if args.impl == "reference":

@@ -244,7 +244,7 @@ def test_attention_alone_at_the_steps_of_the_query_temperature(tmp_path, every):
     folder = zh.make_folder(tmp_path, cfg, seed=every, gain=9.0)
     oracle = zh.Oracle(folder)
     requests = zh.random_requests(cfg, [1, 200, 66, 131], seed=5)
-    engine = build_engine(folder, torch.float32, max_tokens=64 * 4 + 64, max_seqs=2)
+    engine = build_engine(folder, torch.float32, max_tokens=64 * 7, max_seqs=2)
     like = zh.like_config(cfg)
     compare(run_whole(engine, requests), oracle, requests, torch.float32, like, f"temperature every {every} whole")
     compare(run_tail_by_one(engine, requests, tail=140), oracle, requests, torch.float32, like, f"temperature every {every} decoded")
@@ -260,12 +260,10 @@ def test_latent_attention_alone_with_queries_straight_from_the_stream(tmp_path, 
     and cache rows wider than 256."""
     H, dn, dr, dv, rank = shape
     cfg = zh.config(101, 32, [zh.latent(H, dn, dr, dv, rank, base=700.0)], mult=0.8)
-    if not dr:
-        del cfg["layers"][0]["mixer"]["rot"]
     folder = zh.make_folder(tmp_path, cfg, seed=rank, gain=9.0)
     oracle = zh.Oracle(folder)
     requests = zh.random_requests(cfg, [1, 200, 66, 131], seed=5)
-    engine = build_engine(folder, torch.float32, max_tokens=64 * 4 + 64, max_seqs=2)
+    engine = build_engine(folder, torch.float32, max_tokens=64 * 7, max_seqs=2)
     like = zh.like_config(cfg)
     compare(run_whole(engine, requests), oracle, requests, torch.float32, like, f"latent {shape} whole")
     compare(run_tail_by_one(engine, requests, tail=140), oracle, requests, torch.float32, like, f"latent {shape} decoded")
@@ -389,13 +387,13 @@ def test_a_recurrent_channel_that_remembers_the_first_token(tmp_path):
     # what the first token wrote is still felt 300 tokens later, and a sequence that lost its state is units away
     assert np.abs(oracle.logits(requests[0])[-1] - oracle.logits(other)[-1]).max() > 20 * tol
     assert np.abs(oracle.logits(requests[0])[-1] - oracle.logits(requests[0][-1:])[-1]).max() > 1e4 * tol
-    engine = build_engine(folder, torch.float32, max_tokens=64 * 4, max_seqs=3)
+    engine = build_engine(folder, torch.float32, max_tokens=64 * 8, max_seqs=3)
     assert engine.cache.group_keys == []
     compare(run_whole(engine, requests), oracle, requests, torch.float32, like, "recurrent only whole")
     compare(run_tail_by_one(engine, requests, tail=250), oracle, requests, torch.float32, like, "recurrent only decoded")
     compare(run_chunked(engine, requests, [2, 63, 1, 130, 2]), oracle, requests, torch.float32, like, "recurrent only portions")
     compare(run_batches(engine, requests, [[0, 1, 2]], [30, 1, 40]), oracle, requests, torch.float32, like, "recurrent only together")
-    compare(run_batches(engine, requests, [[2, 0], [1]], [90, 280, 2]), oracle, requests, torch.float32, like, "recurrent only slots again")
+    compare(run_batches(engine, requests, [[2, 0], [1]], [280, 2, 90]), oracle, requests, torch.float32, like, "recurrent only slots again")
     assert not engine.cache.live_slots
 
 
