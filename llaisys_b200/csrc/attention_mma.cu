@@ -76,7 +76,22 @@ struct MmaAttnParams {
     int pinned;             // cache pages ahead of the ring that are never overwritten
     int sink;               // the softmax's denominator has one more term e^0 (no value)
     const float* sink_logits;   // [nh] or null: that term is e^(sink_logits[head]) instead (implies a sink)
+    const float* dist_r1;   // [nh] or null: the score of query position i and key position j loses
+    const float* dist_r2;   //   dist_r1[head] * ln(1 + dist_r2[head] * (i - j))
+    float q_temp_coef;      // with q_temp_every > 0: the query at position p is multiplied by
+    int q_temp_every;       //   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)
 };
+
+// What a thread's two score rows need beyond the common scale when scores depend on the positions themselves: the
+// rows' query positions, their scales (the query temperature folded in, base-2 scale) and their heads' two numbers.
+struct RowBias {
+    int q0, q1;
+    float sc0, sc1;
+    float r1a, r2a, r1b, r2b;
+};
+__device__ __forceinline__ float query_temperature(const MmaAttnParams& p, int pos) {
+    return p.q_temp_every > 0 ? 1.f + p.q_temp_coef * logf((float)((pos + 1) / p.q_temp_every) + 1.f) : 1.f;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -238,10 +253,10 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int la
 // One warp: scores of its 16 rows against NT*8 keys starting at row `key0` of the tile in `stage`,
 // masking, online softmax update, and O += P V.  lo0/hi0 and lo1/hi1: visible key positions of
 // the thread's two rows (lane/4 and lane/4 + 8).
-template <int NT, bool MASKED = true>
+template <int NT, bool MASKED = true, bool BIAS = false>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4], float (&m)[2],
                                           float (&l)[2], uint32_t stage, int key0, int pos0, int lo0, int hi0, int lo1,
-                                          int hi1, float scale_log2, int lane, int keep = 0) {
+                                          int hi1, float scale_log2, int lane, int keep = 0, const RowBias rb = RowBias{}) {
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -259,19 +274,30 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
     }
     // mask and row maxima (MASKED = false: the caller knows every key of the tile is visible to every row)
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    const float sc0 = BIAS ? rb.sc0 : scale_log2, sc1 = BIAS ? rb.sc1 : scale_log2;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
         if (MASKED) {
             int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
-            s[n][0] = ((kp >= lo0 || kp < keep) && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
-            s[n][1] = ((kp + 1 >= lo0 || kp + 1 < keep) && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
-            s[n][2] = ((kp >= lo1 || kp < keep) && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
-            s[n][3] = ((kp + 1 >= lo1 || kp + 1 < keep) && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
+            s[n][0] = ((kp >= lo0 || kp < keep) && kp <= hi0) ? s[n][0] * sc0 : -INFINITY;
+            s[n][1] = ((kp + 1 >= lo0 || kp + 1 < keep) && kp + 1 <= hi0) ? s[n][1] * sc0 : -INFINITY;
+            s[n][2] = ((kp >= lo1 || kp < keep) && kp <= hi1) ? s[n][2] * sc1 : -INFINITY;
+            s[n][3] = ((kp + 1 >= lo1 || kp + 1 < keep) && kp + 1 <= hi1) ? s[n][3] * sc1 : -INFINITY;
         } else {
-            s[n][0] *= scale_log2;
-            s[n][1] *= scale_log2;
-            s[n][2] *= scale_log2;
-            s[n][3] *= scale_log2;
+            s[n][0] *= sc0;
+            s[n][1] *= sc0;
+            s[n][2] *= sc1;
+            s[n][3] *= sc1;
+        }
+        if (BIAS) {
+            // r1 ln(1 + r2 d) on the base-2 scale is r1 log2(1 + r2 d); d = 0 costs nothing; masked scores stay -inf
+            const int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
+            const float d0 = (float)max(rb.q0 - kp, 0), d0n = (float)max(rb.q0 - kp - 1, 0);
+            const float d1 = (float)max(rb.q1 - kp, 0), d1n = (float)max(rb.q1 - kp - 1, 0);
+            s[n][0] -= rb.r1a * __log2f(fmaf(rb.r2a, d0, 1.f));
+            s[n][1] -= rb.r1a * __log2f(fmaf(rb.r2a, d0n, 1.f));
+            s[n][2] -= rb.r1b * __log2f(fmaf(rb.r2b, d1, 1.f));
+            s[n][3] -= rb.r1b * __log2f(fmaf(rb.r2b, d1n, 1.f));
         }
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
@@ -392,7 +418,7 @@ __device__ __forceinline__ void cluster_merge(int S, int n_heads, uint32_t ml_ad
 }
 
 // ------------------------------------------------------------------ decode
-template <int NST>
+template <int NST, bool BIAS = false>
 __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -530,6 +556,16 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
+    RowBias rb = RowBias{};
+    if (BIAS) {                                            // rows are the group's heads, all at the new token's position
+        const int ha = head0 + min(lane >> 2, n_heads - 1), hb = head0 + min((lane >> 2) + 8, n_heads - 1);
+        rb.q0 = rb.q1 = pos;
+        rb.sc0 = rb.sc1 = scale_log2 * query_temperature(p, pos);
+        rb.r1a = p.dist_r1 ? p.dist_r1[ha] : 0.f;
+        rb.r2a = p.dist_r2 ? p.dist_r2[ha] : 0.f;
+        rb.r1b = p.dist_r1 ? p.dist_r1[hb] : 0.f;
+        rb.r2b = p.dist_r2 ? p.dist_r2[hb] : 0.f;
+    }
 
     for (int i = 0; i < n_tiles; ++i) {
         const size_t off_now = off_ahead;                  // page of tile i + NST, looked up a pass ago
@@ -554,7 +590,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             __syncthreads();
         }
         zero_unfetched_rows(ring.stage_ptr(i), TILE_AT(i), src.lo_of(TILE_AT(i), key_lo), pos, warp, lane);
-        tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, TILE_AT(i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane, keep);
+        tile_step<2, true, BIAS>(qf, o, m, l, ring.stage(i), warp * 16, TILE_AT(i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane, keep, rb);
         __syncwarp();                                      // the warp's rows of the stage are free
         if (i + NST < n_tiles) issue_tile_rows(src, TILE_AT(i + NST), src.lo_of(TILE_AT(i + NST), key_lo), fetch_hi, ring.stage(i + NST), warp, lane, off_now);
         cp_async_commit();
@@ -742,6 +778,7 @@ __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __r
 }
 
 // ------------------------------------------------------------------ prefill
+template <bool BIAS>
 __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -790,6 +827,15 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
+    RowBias rb = RowBias{};
+    if (BIAS) {
+        rb.q0 = hi0;
+        rb.q1 = hi1;
+        rb.sc0 = scale_log2 * query_temperature(p, hi0);
+        rb.sc1 = scale_log2 * query_temperature(p, hi1);
+        rb.r1a = rb.r1b = p.dist_r1 ? p.dist_r1[head] : 0.f;
+        rb.r2a = rb.r2b = p.dist_r2 ? p.dist_r2[head] : 0.f;
+    }
 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES_PREFILL - 1>();
@@ -798,13 +844,13 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
         zero_unfetched(ring.stage_ptr(i), tile, src.lo_of(tile, key_lo), PTILE_HI(i), tid);
         if (i < n_kept) {
             // kept keys that lie before every row's window: all rows see the keys below `keep` and nothing else here
-            tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, 0, keep - 1, 0, keep - 1, scale_log2, lane);
+            tile_step<8, true, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, 0, keep - 1, 0, keep - 1, scale_log2, lane, 0, rb);
         } else if (p0 <= warp_hi && (p0 + TILE - 1 >= warp_lo || p0 < keep)) {   // the tile holds a key some row of the warp sees
             // every key of the tile visible to every row of the warp (most tiles of a causal prompt): no masks
             const bool all_visible = p0 + TILE - 1 <= first_pos + warp * 16 &&
                                      (p.window <= 0 || p0 >= first_pos + warp * 16 + 15 - p.window + 1);
-            if (all_visible) tile_step<8, false>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
-            else tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, keep);
+            if (all_visible) tile_step<8, false, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, 0, rb);
+            else tile_step<8, true, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, keep, rb);
         }
         __syncthreads();
         if (i + STAGES_PREFILL < n_tiles)
@@ -853,9 +899,16 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
     dim3 grid(p.nh, (max_new + 63) / 64, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    int rc = configure<0>(attn_mma_prefill_kernel, smem_bytes(STAGES_PREFILL));
+    if (p.dist_r1 || p.dist_r2 || p.q_temp_every > 0) {          // scores that depend on the positions themselves
+        if (!p.dist_r1 != !p.dist_r2) return (int)cudaErrorInvalidValue;
+        int rc = configure<2>(attn_mma_prefill_kernel<true>, smem_bytes(STAGES_PREFILL));
+        if (rc) return rc;
+        llb_launch(attn_mma_prefill_kernel<true>, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
+        return llb_status();
+    }
+    int rc = configure<0>(attn_mma_prefill_kernel<false>, smem_bytes(STAGES_PREFILL));
     if (rc) return rc;
-    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
+    llb_launch(attn_mma_prefill_kernel<false>, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
     return llb_status();
 }
 
@@ -890,16 +943,15 @@ LLB_API int llb_attn_mma_decode_max_clusters(int size) {
 
 LLB_DEFINE_SET_STAMPS
 
-LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
-    if (B == 0) return 0;
-    if (!aligned_ok(p) || p.n_splits < 1 || p.n_splits > 64) return (int)cudaErrorInvalidValue;
-    if (p.cluster && p.n_splits > MAX_CLUSTER) return (int)cudaErrorInvalidValue;
+namespace {
+template <bool BIAS>
+int launch_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     int G = p.nh / p.nkvh;
     dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    auto kernel = attn_mma_decode_kernel<STAGES>;
+    auto kernel = attn_mma_decode_kernel<STAGES, BIAS>;
     const int smem = smem_bytes_decode(STAGES);
-    int rc = configure<1>(kernel, smem);
+    int rc = configure<BIAS ? 3 : 1>(kernel, smem);
     if (rc) return rc;
     if (p.cluster && p.n_splits > 8) {
         static bool allowed = false;
@@ -940,4 +992,16 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
         rc = llb_status();
     }
     return rc;
+}
+}  // namespace
+
+LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
+    if (B == 0) return 0;
+    if (!aligned_ok(p) || p.n_splits < 1 || p.n_splits > 64) return (int)cudaErrorInvalidValue;
+    if (p.cluster && p.n_splits > MAX_CLUSTER) return (int)cudaErrorInvalidValue;
+    if (p.dist_r1 || p.dist_r2 || p.q_temp_every > 0) {          // scores that depend on the positions themselves
+        if (!p.dist_r1 != !p.dist_r2) return (int)cudaErrorInvalidValue;
+        return launch_decode<true>(p, B, stream);
+    }
+    return launch_decode<false>(p, B, stream);
 }

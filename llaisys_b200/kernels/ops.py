@@ -705,7 +705,8 @@ class _MmaAttnParams(ctypes.Structure):
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
                 ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
                 ("append_new", c_int), ("cluster", c_int), ("err", c_void_p),
-                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int), ("sink_logits", c_void_p)]
+                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int), ("sink_logits", c_void_p),
+                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -780,8 +781,9 @@ class AttnExtras:
     value-less sink term in the softmax's denominator: of score 0 (`sink`), or of a learned score per query head
     (`sink_logits`, float32 [heads]); a penalty on distance, `dist_bias` = (r1, r2), float32 [heads] each: the score of
     query position i and key position j loses r1[h] ln(1 + r2[h] (i - j)); a query temperature, `q_temp` = (coef, every):
-    the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  The last two run on the CUDA-core
-    kernel (both precisions)."""
+    the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  The last two run on the mma.sync
+    kernels (bfloat16, keys and values of one width that is a multiple of 16 up to 128) and on the CUDA-core kernel (every
+    other case, both precisions), not on the tcgen05 prefill kernel."""
     value_dim: Optional[int] = None
     keep_first: int = 0
     pinned: int = 0
@@ -812,8 +814,8 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
             assert extras.sink_logits.dtype == torch.float32 and extras.sink_logits.numel() == nh
             p.sink_logits = extras.sink_logits.data_ptr()
         if extras.positional():
-            if cls is not None and cls is not _AttnParams:
-                raise KernelError("attention: a distance penalty or a query temperature needs the CUDA-core kernel")
+            if cls is not None and cls not in (_AttnParams, _MmaAttnParams):
+                raise KernelError("attention: a distance penalty or a query temperature needs the CUDA-core or the mma.sync kernel")
             if extras.dist_bias is not None:
                 r1, r2 = extras.dist_bias
                 assert r1.dtype == r2.dtype == torch.float32 and r1.numel() == r2.numel() == nh and r1.is_cuda and r2.is_cuda
@@ -943,8 +945,9 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
                               window, scale, 0, extras.keep_first, extras.sink)
         return out
-    if dv == dh and _mma_ok(qkv, dh) and not extras.positional():
+    if dv == dh and _mma_ok(qkv, dh):
         # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention
+        # (a distance penalty and a query temperature are applied to the score fragments in registers)
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
                          _MmaAttnParams, extras=extras)
         p.all_from_cache = int(all_from_cache)

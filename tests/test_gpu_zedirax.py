@@ -253,6 +253,42 @@ def test_attention_alone_at_the_steps_of_the_query_temperature(tmp_path, every):
     assert not engine.cache.live_slots
 
 
+@pytest.mark.parametrize("dim", [32, 64, 128])
+@pytest.mark.parametrize("every", [64, 65, 1])
+def test_tensor_core_attention_with_penalty_and_temperature_against_the_cuda_core_one(tmp_path, dim, every, monkeypatch):
+    """bfloat16, keys and values of one width: prompts and single tokens run on the mma.sync kernels, which take the
+    penalty off the score fragments and fold the temperature into the rows' scales; with that path switched off the same
+    steps run on the CUDA cores.  Both get the same bfloat16 queries, keys and values, so with sharp scores (a lost key, a
+    distance one off or a temperature at the wrong row would show) they may differ only by the rounding of the
+    probabilities, and both agree with the plain implementation.  Groups of 2, 3 and 12 query heads a key/value head."""
+    from llaisys_b200.kernels import ops
+    cfg = zh.config(101, 32, [zh.attention(4, 2, dim, dim, q_temp=(0.9, every)), zh.attention(3, 1, 16, 16),
+                              zh.attention(12, 1, 32, 32, q_temp=(0.5, 7), mlp=zh.dense(40))], mult=0.8)
+    folder = zh.make_folder(tmp_path, cfg, seed=every + dim, gain=zh.GAIN[torch.bfloat16])
+    oracle = zh.Oracle(folder)
+    requests = zh.random_requests(cfg, [1, 200, 66, 131], seed=5)
+    got, used = {}, {}
+    real = ops._mma_lib
+    for mma in (True, False):
+        calls = []
+        monkeypatch.setattr(ops, "MMA_ATTENTION", mma)
+        monkeypatch.setattr(ops, "_mma_lib", lambda dh, calls=calls: (calls.append(dh), real(dh))[1])
+        engine = build_engine(folder, torch.bfloat16, max_tokens=64 * 7, max_seqs=2)
+        got[mma] = [run_whole(engine, requests), run_tail_by_one(engine, requests, tail=140), run_chunked(engine, requests, [63, 2, 65, 1, 64]),
+                    run_batches(engine, requests, [[1, 3], [0, 2]], [1, 100, 30, 70])]
+        used[mma] = set(calls)
+        for g in got[mma]:
+            compare_zx(g, oracle, requests, torch.bfloat16, cfg, f"tensor cores {mma}, every {every}, head size {dim}")
+        assert not engine.cache.live_slots
+    assert used[True] == {dim, 16, 32} and not used[False]
+    for a, b in zip(got[True], got[False]):
+        for key in b:
+            ref = b[key].astype(np.float64)
+            rms = np.sqrt((ref ** 2).mean())
+            d = a[key] - ref
+            assert np.sqrt((d ** 2).mean()) <= 0.03 * rms + 2e-4, (every, dim, key)
+
+
 @pytest.mark.parametrize("shape", [(3, 8, 8, 12, 24), (2, 0, 16, 8, 12), (4, 12, 0, 6, 300), (1, 6, 4, 20, 9)])
 def test_latent_attention_alone_with_queries_straight_from_the_stream(tmp_path, shape):
     """One latent layer without a feed-forward, float32: no query latent, a gate on every element of the heads' outputs,
