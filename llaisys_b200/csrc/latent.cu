@@ -357,9 +357,31 @@ __global__ void head_gate_vec_kernel(bf16* __restrict__ x, const bf16* __restric
     reinterpret_cast<uint4*>(x)[i] = v;
 }
 
+// bfloat16, one gate an element (heads of width 1), rows of a multiple of 8 elements, both 16-byte aligned: a thread takes
+// eight neighbouring elements and their eight gates
+__global__ void elem_gate_vec_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, int gate_stride, int H8, size_t n8) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const size_t t = i / H8;
+    const int c = (int)(i - t * H8);
+    uint4 v = reinterpret_cast<uint4*>(x)[i];
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate + t * gate_stride + (size_t)c * 8);
+    bf16* e = reinterpret_cast<bf16*>(&v);
+    const bf16* g = reinterpret_cast<const bf16*>(&gv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) e[k] = __float2bfloat16_rn(__bfloat162float(e[k]) / (1.0f + expf(-__bfloat162float(g[k]))));
+    reinterpret_cast<uint4*>(x)[i] = v;
+}
+
 LLB_API int llb_head_gate(void* x, const void* gate, int gate_stride, int dtype, int T, int H, int width, cudaStream_t stream) {
     size_t n = (size_t)T * H * width;
     if (n == 0) return 0;
+    if (dtype == LLB_BF16 && width == 1 && H % 8 == 0 && gate_stride % 8 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)gate & 15)) {
+        llb_launch(elem_gate_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate,
+                   gate_stride, H / 8, n / 8);
+        return llb_status();
+    }
     if (dtype == LLB_BF16 && width % 8 == 0 && !((uintptr_t)x & 15)) {
         llb_launch(head_gate_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate,
                    gate_stride, H, width / 8, n / 8);

@@ -29,6 +29,8 @@ struct MinGruParams {
     int chunk, n_chunks;
 };
 
+#define MG_AHEAD 8            // tokens whose loads a thread has in flight
+
 __device__ __forceinline__ float mg_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float mg_candidate(float u) { return u >= 0.f ? u + 0.5f : mg_sigmoid(u); }
 
@@ -38,18 +40,19 @@ __device__ __forceinline__ float mg_run(const MinGruParams& p, int ch, int t0, i
     const TI* proj = (const TI*)p.proj;
     TO* out = (TO*)p.out;
     int t = t0;
-    // four tokens' loads are requested before the first is used: the recurrence itself is a few dependent operations
-    for (; t + 4 <= t1; t += 4) {
-        float a[4], u[4], g[4];
+    // eight tokens' loads are requested before the first is used: the recurrence itself is a few dependent operations,
+    // and a long prompt's chunks fill only part of the SMs' warps
+    for (; t + MG_AHEAD <= t1; t += MG_AHEAD) {
+        float a[MG_AHEAD], u[MG_AHEAD], g[MG_AHEAD];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < MG_AHEAD; ++i) {
             const TI* row = proj + (size_t)(t + i) * p.ld;
             a[i] = to_f32(row[p.a_off + ch]);
             u[i] = to_f32(row[p.u_off + ch]);
             if (WRITE) g[i] = to_f32(row[p.g_off + ch]);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < MG_AHEAD; ++i) {
             const float z = mg_sigmoid(a[i]);
             S = fmaf(z, mg_candidate(u[i]) - S, S);            // (1 - z) S + z c
             if (WRITE) out[(size_t)(t + i) * p.width + ch] = from_f32<TO>(S * g[i] * mg_sigmoid(g[i]));
@@ -91,16 +94,16 @@ __global__ void __launch_bounds__(128) mingru_reduce_kernel(MinGruParams p) {
     const TI* proj = (const TI*)p.proj;
     float A = 1.f, B = 0.f;
     int t = t0;
-    for (; t + 4 <= t1; t += 4) {
-        float a[4], u[4];
+    for (; t + MG_AHEAD <= t1; t += MG_AHEAD) {
+        float a[MG_AHEAD], u[MG_AHEAD];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < MG_AHEAD; ++i) {
             const TI* row = proj + (size_t)(t + i) * p.ld;
             a[i] = to_f32(row[p.a_off + ch]);
             u[i] = to_f32(row[p.u_off + ch]);
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < MG_AHEAD; ++i) {
             const float z = mg_sigmoid(a[i]);
             A *= 1.f - z;
             B = fmaf(z, mg_candidate(u[i]) - B, B);
@@ -127,8 +130,24 @@ __global__ void __launch_bounds__(128) mingru_prefix_kernel(MinGruParams p) {
     const int chunks = (n_new + p.chunk - 1) / p.chunk;
     float* st = p.state + (size_t)p.seq_slot[b] * p.width + ch;
     float S = *st;
-    for (int k = 0; k < chunks; ++k) {
-        const size_t i = ((size_t)b * p.n_chunks + k) * p.width + ch;
+    const size_t base = (size_t)b * p.n_chunks * p.width + ch;
+    int k = 0;
+    // eight chunks' pairs are fetched together (the walk itself is one multiply-add a chunk, a load's latency each otherwise)
+    for (; k + 8 <= chunks; k += 8) {
+        float A[8], B[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            A[j] = p.chunk_a[base + (size_t)(k + j) * p.width];
+            B[j] = p.chunk_b[base + (size_t)(k + j) * p.width];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            p.chunk_a[base + (size_t)(k + j) * p.width] = S;
+            S = fmaf(A[j], S, B[j]);
+        }
+    }
+    for (; k < chunks; ++k) {
+        const size_t i = base + (size_t)k * p.width;
         const float A = p.chunk_a[i], B = p.chunk_b[i];
         p.chunk_a[i] = S;
         S = fmaf(A, S, B);
