@@ -462,6 +462,24 @@ def test_sizes_that_the_usual_models_make_equal_or_one(tmp_path):
         compare(run_batches(engine, requests, [[0, 1, 2]], [50, 1, 3]), oracle, requests, torch.float32, like, f"sizes {i} together")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(70, 6, 1, 0), (70, 40, 1, 8), (33, 24, 1, 3), (5, 3, 16, 0), (9, 4, 12, 4)])
+def test_gate_of_the_heads_by_head_and_by_element(dtype, shape):
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place, the gate a view into a wider buffer: heads of one element (a gate an element;
+    rows of a multiple of eight on a 16-byte boundary go in 16-byte pieces, others one by one) and wider heads."""
+    from llaisys_b200 import kernels
+    T, H, width, off = shape
+    rng = np.random.default_rng(T + H)
+    x = _bf16_exact(rng.normal(size=(T, H * width)))
+    buf = _bf16_exact(rng.normal(size=(T, off + H + 8)) * 3)
+    xd, bd = _dev(x, dtype), _dev(buf, dtype)
+    kernels.head_gate_(xd, bd[:, off:], H)
+    want = (x.reshape(T, H, width) / (1 + np.exp(-buf[:, off:off + H]))[:, :, None]).reshape(T, H * width)
+    got = xd.float().cpu().numpy().astype(np.float64)
+    bound = 1e-6 if dtype == torch.float32 else 2.0 ** -8
+    assert np.abs(got - want).max() <= bound * max(1.0, np.abs(want).max())
+
+
 # ----------------------------------------------------------------------------- whole models under every schedule
 LENGTHS = {"P": [1, 2, 64, 71, 150, 300], "Q": [3, 65, 129, 40], "R": [1, 66, 67, 200, 131]}
 
