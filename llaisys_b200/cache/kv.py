@@ -88,8 +88,8 @@ class PagedCache:
                 if needs[owner].window is not None:
                     raise CacheError(f"call {c} reads the cache of call {owner}, which keeps a window only; "
                                      f"a shared cache has to keep every key")
-                if need is not None and (need.num_kv_heads, need.key_dim, need.value_dim) != (
-                        needs[owner].num_kv_heads, needs[owner].key_dim, needs[owner].value_dim):
+                if need is not None and (need.num_kv_heads, need.key_dim, need.value_dim, need.every) != (
+                        needs[owner].num_kv_heads, needs[owner].key_dim, needs[owner].value_dim, needs[owner].every):
                     raise CacheError(f"call {c} reads the cache of call {owner} but their head shapes differ")
                 self.call_group.append(self.call_group[owner])
                 self.call_entry.append(self.call_entry[owner])
@@ -100,8 +100,13 @@ class PagedCache:
                 self.call_group.append(None)
                 self.call_entry.append(None)
                 continue
+            every = max(1, int(need.every))
+            if every > 1 and need.window is not None:
+                raise CacheError(f"call {c} keeps one row per {every} tokens; such rows are all kept (no window)")
             key = (need.num_kv_heads, need.key_dim, need.value_dim, ring_pages(need.window),
                    pinned_pages(need.window, need.keep_first))
+            if every > 1:
+                key += (every,)                       # a group of rows per block of tokens
             if key not in self.group_keys:
                 self.group_keys.append(key)
                 entries_per_group.append(0)
@@ -114,7 +119,8 @@ class PagedCache:
         # a sequence never holds more pages of a window group than its ring and its pinned pages
         self.group_pages = [n_pages if r is None else min(n_pages, (r + p) * self.n_slots)
                             for r, p in zip(self.rings, self.pinned)]
-        self.book = SlotBook(self.n_slots, self.group_pages, self.rings, PAGE, self.pinned)
+        self.every = [k[5] if len(k) > 5 else 1 for k in self.group_keys]
+        self.book = SlotBook(self.n_slots, self.group_pages, self.rings, PAGE, self.pinned, self.every)
         # ---- storage
         self.k_pools: List[torch.Tensor] = []
         self.v_pools: List[torch.Tensor] = []
@@ -122,7 +128,8 @@ class PagedCache:
         self.state_sizes = list(state_sizes)
         self._guards: List[tuple] = []            # (what, raw allocation) of every guarded tensor
         if allocate:
-            for g, ((nkvh, dk, dv, _, _), n_entries, pages) in enumerate(zip(self.group_keys, entries_per_group, self.group_pages)):
+            for g, (key, n_entries, pages) in enumerate(zip(self.group_keys, entries_per_group, self.group_pages)):
+                nkvh, dk, dv = key[:3]
                 self.k_pools.append(self._zeros(f"keys of group {g}", (n_entries, pages, nkvh, PAGE, dk), dtype))
                 self.v_pools.append(self._zeros(f"values of group {g}", (n_entries, pages, nkvh, PAGE, dv), dtype)
                                     if dv > 0 else None)

@@ -66,15 +66,17 @@ class SlotBook:
     pinned: per group, pages ahead of the ring that hold the sequence's first tokens for good: a sequence
     holds min(ceil(n / page), pinned + ring) pages, logical page lp < pinned at entry lp, a later one at
     entry pinned + (lp - pinned) % ring.
+    every: per group, tokens per row (default 1): a group of blocks holds floor(n / every) rows for n tokens.
     """
 
     def __init__(self, n_slots: int, pages_per_group: List[int], rings: List[int | None], page: int,
-                 pinned: List[int] | None = None):
+                 pinned: List[int] | None = None, every: List[int] | None = None):
         assert len(pages_per_group) == len(rings)
         self.page = page
         self.rings = list(rings)
         self.pinned = list(pinned) if pinned is not None else [0] * len(rings)
-        assert len(self.pinned) == len(self.rings)
+        self.every = list(every) if every is not None else [1] * len(rings)
+        assert len(self.pinned) == len(self.rings) == len(self.every)
         self.slots = FreeList(n_slots, "slot")
         self.pools = [FreeList(n, f"page of group {g}") for g, n in enumerate(pages_per_group)]
         self.seqs: Dict[int, Sequence] = {}
@@ -104,7 +106,7 @@ class SlotBook:
 
     # ---- pages
     def pages_needed(self, group: int, length: int) -> int:
-        n = -(-length // self.page)
+        n = -(-(length // self.every[group]) // self.page)
         ring = self.rings[group]
         return n if ring is None else min(n, ring + self.pinned[group])
 

@@ -59,9 +59,11 @@ class CallSpec:
     """One entry of the run order.  `layer` indexes `ModelSpec.layers` and may repeat.
     `cache_of` names an earlier entry of the order whose cache this call's mixers read instead of
     keeping one of their own (they then append nothing); the mixers of the two entries pair up in
-    sub-layer order."""
+    sub-layer order.  `opens_pass` t: this entry is the first of pass t (0, 1, ...) over a run of layers that the model
+    repeats; the model's `reentry` part adds what a pass starts with to the stream before the entry runs."""
     layer: int
     cache_of: Optional[int] = None
+    opens_pass: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -76,6 +78,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
+    reentry: Optional[PartSpec] = None        # what is added to the stream where an entry of the order opens a pass
 
 
 class ConfigError(ValueError):

@@ -73,6 +73,17 @@ struct AttnParams {
     const float* dist_r2;
     float q_temp_coef;    // with q_temp_every > 0 the query at position p is multiplied by
     int q_temp_every;     //   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)
+    int chunk;            // > 0: a query at position p sees no key before floor(p / chunk) * chunk
+    int maps;             // > 1: `maps` key heads share one value head; nkvh counts key heads, the cache has nkvh / maps
+                          //      heads whose key rows hold the maps' keys side by side (maps * DH elements)
+    int out_f32;          // out is float32 whatever the operands' type
+    int pool;             // > 0 (with a window): beside the window's keys, one key and value per block of `pool` positions
+                          //      that lies wholly before the window (block b: b * pool + pool - 1 <= p - window), read
+                          //      at row b of a second cache; tokens and blocks share one softmax
+    const void* pool_k;   // [pages, nkvh / maps, LLB_PAGE, maps * DH]
+    const void* pool_v;   // [pages, nkvh / maps, LLB_PAGE, DV]
+    const int* pool_table;  // [B, pool_table_stride]
+    int pool_table_stride;
 };
 
 template <typename T, bool DECODE>
@@ -93,6 +104,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     const int n_new = p.seq_start[b + 1] - tok0;
     const int len_before = p.seq_len_before[b];
     const int G = p.nh / p.nkvh;
+    const int maps = p.maps > 1 ? p.maps : 1, cache_heads = p.nkvh / maps, krow = DH * maps;
     const int* table = p.page_table + (size_t)b * p.table_stride;
 
     // ---- the rows of this block: (token, head, position) per row
@@ -116,6 +128,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         first_pos = len_before + t0;
         last_pos = first_pos + n_rows - 1;
     }
+    const int vh = kvh / maps, kmap = kvh - vh * maps;     // the key head's value head and its place in the cache's key row
     const T* qbase = (const T*)p.q;
     for (int i = tid; i < n_rows * DH; i += WARPS * 32) {
         int r = i / DH, d = i - r * DH;
@@ -126,9 +139,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     // ---- key tiles of this block: the tiles of the kept first keys that lie before the window's, then the window's
     const int keep = p.window > 0 ? p.keep_first : 0;
     int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+    if (p.chunk > 0) key_lo = max(key_lo, (first_pos / p.chunk) * p.chunk);
     const int tile_lo = key_lo / LLB_PAGE, tile_hi = last_pos / LLB_PAGE + 1;
     const int n_kept = min((keep + LLB_PAGE - 1) / LLB_PAGE, tile_lo);
-    int it_lo = 0, it_hi = n_kept + tile_hi - tile_lo;        // tile it: it < n_kept ? it : tile_lo + it - n_kept
+    // pooled blocks that the block's last row sees, and their tiles (walked first)
+    const int blocks_hi = (p.pool > 0 && p.window > 0) ? max(0, (last_pos - p.window + 1) / p.pool) : 0;
+    const int n_pool = (blocks_hi + LLB_PAGE - 1) / LLB_PAGE;
+    int it_lo = 0, it_hi = n_pool + n_kept + tile_hi - tile_lo;   // after the pooled tiles: it < n_kept ? it : tile_lo + it - n_kept
     if (DECODE) {
         int chunk = (it_hi + p.n_splits - 1) / p.n_splits;
         it_lo = blockIdx.x * chunk;
@@ -152,18 +169,33 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     const T* vnew = (const T*)p.v_new;
 
     for (int it = it_lo; it < it_hi; ++it) {
-        const int tile = it < n_kept ? it : tile_lo + it - n_kept;
+        const bool pooled = it < n_pool;
+        const int tile = pooled ? it : (it - n_pool < n_kept ? it - n_pool : tile_lo + it - n_pool - n_kept);
         __syncthreads();                     // previous tile fully consumed (and Qs written)
         // A tile is one cache page (tiles start at multiples of LLB_PAGE): its page is looked up once; rows move in
         // 16-byte pieces where the widths and the addresses allow it.
         const int p0 = tile * LLB_PAGE;
         // (the page table is read only for a tile that holds cached positions: a step without history may come with
         // an empty table)
+        if (pooled) {
+            const int* ptab = p.pool_table + (size_t)b * p.pool_table_stride;
+            const T* kp = (const T*)p.pool_k + paged_row(ptab, p.pool_table_stride, p0, vh, cache_heads, krow, 0) + kmap * DH;
+            const T* vp = (const T*)p.pool_v + paged_row(ptab, p.pool_table_stride, p0, vh, cache_heads, DV, 0);
+            for (int i = tid; i < LLB_PAGE * DH; i += WARPS * 32) {
+                const int j = i / DH, d = i - j * DH;
+                Ks[j * (DH + 1) + d] = p0 + j < blocks_hi ? to_f32(kp[(size_t)j * krow + d]) : 0.f;
+            }
+            for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
+                const int j = i / DV, d = i - j * DV;
+                Vs[j * DV + d] = p0 + j < blocks_hi ? to_f32(vp[(size_t)j * DV + d]) : 0.f;
+            }
+        }
         const bool cached = DECODE || p.all_from_cache || p0 < len_before;
-        const T* kpage = cached ? kpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DH, p.pinned) : nullptr;
+        const T* kpage = (cached && !pooled) ? kpool + paged_row(table, p.ring, p0, vh, cache_heads, krow, p.pinned) + kmap * DH : nullptr;
         constexpr int VEC = 16 / (int)sizeof(T);
         const bool kvec = DH % VEC == 0 && (((uintptr_t)kpool | (uintptr_t)knew) & 15) == 0 && kv_stride % VEC == 0;
-        if (kvec) {
+        if (pooled) {
+        } else if (kvec) {
             // eight pieces a thread are requested before the first is used: the walk waits for memory once per batch
             constexpr int PIECES = LLB_PAGE * (DH / VEC), BATCH = 8;
             for (int i0 = tid; i0 < PIECES; i0 += BATCH * WARPS * 32) {
@@ -177,7 +209,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
                         if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
                             const T* src = (!DECODE && !p.all_from_cache && kp >= len_before)
                                                ? knew + (size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d
-                                               : kpage + (size_t)j * DH + d;
+                                               : kpage + (size_t)j * krow + d;
                             raw[u] = *reinterpret_cast<const uint4*>(src);
                         }
                     }
@@ -202,20 +234,20 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
                     if (!DECODE && !p.all_from_cache && kp >= len_before)
                         kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d]);
                     else
-                        kv = to_f32(kpage[(size_t)j * DH + d]);
+                        kv = to_f32(kpage[(size_t)j * krow + d]);
                 }
                 Ks[j * (DH + 1) + d] = kv;
             }
         }
-        if (!p.v_in_k) {
-            const T* vpage = cached ? vpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DV, p.pinned) : nullptr;
+        if (!p.v_in_k && !pooled) {
+            const T* vpage = cached ? vpool + paged_row(table, p.ring, p0, vh, cache_heads, DV, p.pinned) : nullptr;
             for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
                 int j = i / DV, d = i - j * DV;
                 int kp = p0 + j;
                 float vv = 0.f;
                 if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
                     if (!DECODE && !p.all_from_cache && kp >= len_before)
-                        vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DV + d]);
+                        vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * kv_stride + vh * DV + d]);
                     else
                         vv = to_f32(vpage[(size_t)j * DV + d]);
                 }
@@ -229,6 +261,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             if (r >= n_rows) continue;       // uniform within the warp
             int pos = DECODE ? first_pos : first_pos + r;
             int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            if (p.chunk > 0) lo = max(lo, (pos / p.chunk) * p.chunk);
+            const int blocks_seen = pooled ? max(0, (pos - p.window + 1) / p.pool) : 0;
             float row_scale = p.scale;
             if (p.q_temp_every > 0) row_scale *= 1.0f + p.q_temp_coef * logf((float)((pos + 1) / p.q_temp_every + 1));
             float r1 = 0.f, r2 = 0.f;
@@ -262,9 +296,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             float s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]), s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
             int kp0 = tile * LLB_PAGE + lane, kp1 = kp0 + 32;
             bool v0 = (kp0 >= lo || kp0 < keep) && kp0 <= pos, v1 = (kp1 >= lo || kp1 < keep) && kp1 <= pos;
+            if (pooled) {
+                v0 = kp0 < blocks_seen;
+                v1 = kp1 < blocks_seen;
+            }
             s0 = v0 ? s0 * row_scale : -INFINITY;
             s1 = v1 ? s1 * row_scale : -INFINITY;
-            if (p.dist_r1) {
+            if (p.dist_r1 && !pooled) {
                 if (v0) s0 -= r1 * log1pf(r2 * (float)(pos - kp0));
                 if (v1) s1 -= r1 * log1pf(r2 * (float)(pos - kp1));
             }
@@ -300,12 +338,15 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         if (r >= n_rows) continue;
         int tok = row_tok0 + (DECODE ? 0 : r), head = row_head0 + (DECODE ? r : 0);
         if (!DECODE || p.n_splits == 1) {
-            T* out = (T*)p.out + (size_t)tok * p.nh * DV + head * DV;
+            const size_t at = (size_t)tok * p.nh * DV + head * DV;
             float inv = 1.0f / l[i];
 #pragma unroll
             for (int e = 0; e < DPL; ++e) {
                 int d = lane + e * 32;
-                if (d < DV) out[d] = from_f32<T>(o[i][e] * inv);
+                if (d < DV) {
+                    if (p.out_f32) ((float*)p.out)[at + d] = o[i][e] * inv;
+                    else ((T*)p.out)[at + d] = from_f32<T>(o[i][e] * inv);
+                }
             }
         } else {
             size_t slot = ((size_t)b * p.nh + head) * p.n_splits + blockIdx.x;
@@ -371,7 +412,7 @@ static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t stream) {
 // number of new tokens of a sequence in the batch.
 LLB_API int llb_attn_prefill(AttnParams p, int dtype, int B, int max_new, cudaStream_t stream) {
     if (B == 0 || max_new == 0) return 0;
-    if (p.nkvh <= 0 || p.nh % p.nkvh) return (int)cudaErrorInvalidValue;
+    if (p.nkvh <= 0 || p.nh % p.nkvh || (p.maps > 1 && p.nkvh % p.maps)) return (int)cudaErrorInvalidValue;
     dim3 grid((max_new + ROWS - 1) / ROWS, p.nh, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     LLB_DISPATCH_DTYPE(dtype, T, return launch_attn<T, false>(p, grid, stream));
@@ -381,7 +422,7 @@ LLB_API int llb_attn_prefill(AttnParams p, int dtype, int B, int max_new, cudaSt
 // Decode: every sequence has exactly one new token, already in the cache.
 LLB_API int llb_attn_decode(AttnParams p, int dtype, int B, cudaStream_t stream) {
     if (B == 0) return 0;
-    if (p.nkvh <= 0 || p.nh % p.nkvh || p.n_splits < 1) return (int)cudaErrorInvalidValue;
+    if (p.nkvh <= 0 || p.nh % p.nkvh || p.n_splits < 1 || (p.maps > 1 && p.nkvh % p.maps)) return (int)cudaErrorInvalidValue;
     int G = p.nh / p.nkvh;
     dim3 grid(p.n_splits, p.nkvh * ((G + ROWS - 1) / ROWS), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
@@ -389,8 +430,12 @@ LLB_API int llb_attn_decode(AttnParams p, int dtype, int B, cudaStream_t stream)
     LLB_DISPATCH_DTYPE(dtype, T, {
         rc = launch_attn<T, true>(p, grid, stream);
         if (rc == 0 && p.n_splits > 1) {
-            llb_launch(attn_combine_kernel<T>, dim3(p.nh, B), dim3(128), 0, stream,
-                       (T*)p.out, (const float*)p.part_o, (const float*)p.part_ml, p.seq_start, p.nh, p.n_splits);
+            if (p.out_f32)
+                llb_launch(attn_combine_kernel<float>, dim3(p.nh, B), dim3(128), 0, stream,
+                           (float*)p.out, (const float*)p.part_o, (const float*)p.part_ml, p.seq_start, p.nh, p.n_splits);
+            else
+                llb_launch(attn_combine_kernel<T>, dim3(p.nh, B), dim3(128), 0, stream,
+                           (T*)p.out, (const float*)p.part_o, (const float*)p.part_ml, p.seq_start, p.nh, p.n_splits);
             rc = llb_status();
         }
         return rc;

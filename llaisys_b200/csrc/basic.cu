@@ -975,9 +975,15 @@ LLB_API int llb_scaled_norm_add(float* residual, const void* delta, int delta_dt
 }
 
 // ------------------------------------------------------------------ gated activation of a fused gate/up product
-// gate_up is [T, 2I] with the gate columns first; out[t, i] = act(gate) * up, act: 0 silu, 1 relu, 2 gelu (tanh form).
+// gate_up is [T, 2I] with the gate columns first; out[t, i] = act(gate) * up, act: 0 silu, 1 relu, 2 gelu (tanh form);
+// 3: the clamped form g' = min(gate, limit), u' = clamp(up, -limit, limit), out = g' sigmoid(alpha g') (u' + 1).
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
 template <typename TI, typename TO>
-__global__ void glu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_up, int I, size_t n, int act) {
+__global__ void glu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_up, int I, size_t n, int act, float limit, float alpha) {
     llb_grid_dependency_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -985,6 +991,10 @@ __global__ void glu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_up,
     int c = (int)(i - t * I);
     float g = to_f32(gate_up[t * 2 * I + c]);
     float u = to_f32(gate_up[t * 2 * I + I + c]);
+    if (act == 3) {
+        out[i] = from_f32<TO>(glu_clamped(g, u, limit, alpha));
+        return;
+    }
     float a;
     if (act == 1) a = fmaxf(g, 0.f);
     else if (act == 2) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
@@ -998,7 +1008,8 @@ __device__ __forceinline__ float glu_act(float g, int act) {
     if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     return g / (1.0f + expf(-g));
 }
-__global__ void glu_vec_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate_up, int I8, size_t n8, int act) {
+__global__ void glu_vec_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate_up, int I8, size_t n8, int act, float limit,
+                               float alpha) {
     llb_grid_dependency_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n8) return;
@@ -1011,22 +1022,26 @@ __global__ void glu_vec_kernel(bf16* __restrict__ out, const bf16* __restrict__ 
     uint4 o;
     bf16* ov = reinterpret_cast<bf16*>(&o);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) ov[e] = __float2bfloat16_rn(glu_act(__bfloat162float(gv[e]), act) * __bfloat162float(uv[e]));
+    for (int e = 0; e < 8; ++e) {
+        const float gf = __bfloat162float(gv[e]), uf = __bfloat162float(uv[e]);
+        ov[e] = __float2bfloat16_rn(act == 3 ? glu_clamped(gf, uf, limit, alpha) : glu_act(gf, act) * uf);
+    }
     reinterpret_cast<uint4*>(out)[i] = o;
 }
 
-LLB_API int llb_glu(void* out, int out_dtype, const void* gate_up, int in_dtype, int T, int I, int act, cudaStream_t stream) {
+LLB_API int llb_glu(void* out, int out_dtype, const void* gate_up, int in_dtype, int T, int I, int act, float limit, float alpha,
+                    cudaStream_t stream) {
     size_t n = (size_t)T * I;
     if (n == 0) return 0;
     if (in_dtype == LLB_BF16 && out_dtype == LLB_BF16 && I % 8 == 0 && !(((uintptr_t)out | (uintptr_t)gate_up) & 15)) {
         llb_launch(glu_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (bf16*)out, (const bf16*)gate_up,
-                   I / 8, n / 8, act);
+                   I / 8, n / 8, act, limit, alpha);
         return llb_status();
     }
     LLB_DISPATCH_DTYPE(in_dtype, TI, {
         LLB_DISPATCH_DTYPE(out_dtype, TO, {
             llb_launch(glu_kernel<TI, TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TO*)out,
-                       (const TI*)gate_up, I, n, act);
+                       (const TI*)gate_up, I, n, act, limit, alpha);
         });
     });
     return llb_status();

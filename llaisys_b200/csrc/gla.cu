@@ -33,6 +33,8 @@ struct GlaParams {
     int H, dk, dv;
     float q_scale, inv_tau;
     int z_is_decay;           // z already holds a = sigmoid(z)^(1/tau) (llb_gla_decay ran over it)
+    const float* head_decay;  // [H] or null: one constant decay a head, the same for every token and key channel (z is not read)
+    int act;                  // 1: q, k and v pass through silu on their way in
 };
 
 // log sigmoid(z) = -softplus(-z) = -(max(-z, 0) + log(1 + e^-|z|));  a = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau)
@@ -92,25 +94,28 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
     constexpr int NQ = (GLA_CHUNK * DKP + GLA_THREADS - 1) / GLA_THREADS;
     constexpr int NV = (GLA_CHUNK * COLS + GLA_THREADS - 1) / GLA_THREADS;
     float rq[NQ], rk[NQ], rz[NQ], rv[NV];
+    const bool is_decay = p.z_is_decay || p.head_decay;
+    const float head_a = p.head_decay ? p.head_decay[h] : 0.f;
+    auto act = [&](float x) { return p.act == 1 ? x / (1.0f + expf(-x)) : x; };
     auto fetch = [&](int c0) {
         const int nc = min(GLA_CHUNK, n - c0);
 #pragma unroll
         for (int e = 0; e < NQ; ++e) {
             const int idx = tid + e * GLA_THREADS, t = idx / DKP, i = idx - t * DKP;
             rq[e] = rk[e] = 0.f;
-            rz[e] = p.z_is_decay ? 1.f : INFINITY;         // a decay of exactly one
+            rz[e] = is_decay ? 1.f : INFINITY;             // a decay of exactly one
             if (idx < GLA_CHUNK * DKP && i < dk && t < nc) {
                 const size_t row = (size_t)(tok0 + c0 + t);
-                rq[e] = to_f32(qb[row * p.row_stride + h * dk + i]);
-                rk[e] = to_f32(kb[row * p.row_stride + h * dk + i]);
-                rz[e] = p.z[row * p.z_stride + h * dk + i];
+                rq[e] = act(to_f32(qb[row * p.row_stride + h * dk + i]));
+                rk[e] = act(to_f32(kb[row * p.row_stride + h * dk + i]));
+                rz[e] = p.head_decay ? head_a : p.z[row * p.z_stride + h * dk + i];
             }
         }
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
             const int idx = tid + e * GLA_THREADS, t = idx / COLS, c = idx - t * COLS;
             const int cc = blockIdx.x * COLS + c;
-            rv[e] = (idx < GLA_CHUNK * COLS && cc < dv && t < nc) ? to_f32(vb[(size_t)(tok0 + c0 + t) * p.row_stride + h * dv + cc]) : 0.f;
+            rv[e] = (idx < GLA_CHUNK * COLS && cc < dv && t < nc) ? act(to_f32(vb[(size_t)(tok0 + c0 + t) * p.row_stride + h * dv + cc])) : 0.f;
         }
     };
     fetch(0);
@@ -127,7 +132,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
                 const int at = t * ROW + (i / KPT) * (KPT + PAD) + (i % KPT);
                 sq[at] = rq[e] * p.q_scale;
                 sk[at] = rk[e];
-                sa[at] = p.z_is_decay ? rz[e] : gla_decay(rz[e], p.inv_tau);
+                sa[at] = is_decay ? rz[e] : gla_decay(rz[e], p.inv_tau);
             }
         }
 #pragma unroll
@@ -229,11 +234,11 @@ LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, int sms, cudaStream_t st
     return 0;
 }
 
-// out[t, h * dv + d] = o[t, h, d] / sqrt(mean_d o[t, h, :]^2 + eps) * w[d] * silu(g[t, h * dv + d])
+// out[t, h * dv + d] = o[t, h, d] / sqrt(mean_d o[t, h, :]^2 + eps) * w[d] * silu(g[t, h * dv + d])      (gate_act 1: sigmoid(g))
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) gla_out_kernel(const float* __restrict__ o, const T* __restrict__ g, int g_stride,
                                                       const TW* __restrict__ w, T* __restrict__ out, int rows, int H, int dv,
-                                                      float eps) {
+                                                      float eps, int gate_act) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);       // (token, head)
     llb_grid_dependency_sync();
@@ -246,18 +251,19 @@ __global__ void __launch_bounds__(128) gla_out_kernel(const float* __restrict__ 
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int d = lane; d < dv; d += 32) {
         float gv = to_f32(g[(size_t)t * g_stride + h * dv + d]);
-        out[(size_t)r * dv + d] = from_f32<T>(x[d] * inv * to_f32(w[d]) * (gv / (1.0f + expf(-gv))));
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        out[(size_t)r * dv + d] = from_f32<T>(x[d] * inv * to_f32(w[d]) * (gate_act == 1 ? sg : gv * sg));
     }
 }
 
 LLB_API int llb_gla_out(const float* o, const void* g, int g_stride, const void* w, int w_dtype, void* out, int dtype,
-                        int T, int H, int dv, float eps, cudaStream_t stream) {
+                        int T, int H, int dv, float eps, int gate_act, cudaStream_t stream) {
     int rows = T * H;
     if (rows == 0) return 0;
     LLB_DISPATCH_DTYPE(dtype, TT, {
         LLB_DISPATCH_DTYPE(w_dtype, TW, {
             llb_launch(gla_out_kernel<TT, TW>, dim3((rows + 3) / 4), dim3(128), 0, stream, o, (const TT*)g, g_stride,
-                       (const TW*)w, (TT*)out, rows, H, dv, eps);
+                       (const TW*)w, (TT*)out, rows, H, dv, eps, gate_act);
         });
     });
     return llb_status();

@@ -22,8 +22,9 @@ constexpr int MOE_TILE = 64;
 // arg-max (ties to the lower index), weights g * route_scale.
 __global__ void __launch_bounds__(128)
 moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int T, int E, int top, float route_scale,
-                  int* __restrict__ idx, float* __restrict__ wgt, int mode) {
+                  int* __restrict__ idx, float* __restrict__ wgt, int mode, int n_groups, int keep_groups, int renorm) {
     extern __shared__ float sm[];                 // per warp: gate[E], choice[E]
+    __shared__ float group_score[4][64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     float* gate = sm + (size_t)warp * 2 * E;
@@ -37,6 +38,35 @@ moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
         choice[e] = g + (bias ? bias[e] : 0.f);
     }
     __syncwarp();
+    if (n_groups > 1) {
+        // the experts form n_groups equal groups of neighbours; a group's score is the sum of its two largest choice
+        // scores; only experts of the keep_groups best groups (first maximum first) stay in the choice
+        const int per = E / n_groups;
+        float* gs = group_score[warp];
+        for (int g = lane; g < n_groups; g += 32) {
+            float b0 = -INFINITY, b1 = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float c = choice[e];
+                if (c > b0) { b1 = b0; b0 = c; }
+                else if (c > b1) b1 = c;
+            }
+            gs[g] = per > 1 ? b0 + b1 : b0;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int k = 0; k < keep_groups; ++k) {
+                int arg = -1;
+                float best = -INFINITY;
+                for (int g = 0; g < n_groups; ++g)
+                    if (gs[g] != INFINITY && (arg < 0 || gs[g] > best)) { best = gs[g]; arg = g; }
+                if (arg >= 0) gs[arg] = INFINITY;          // kept
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
@@ -75,15 +105,25 @@ moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
         const float inv = route_scale / sum;
         for (int k = 0; k < top; ++k) w[k] *= inv;
     }
+    if (mode != 1 && renorm && lane == 0) {
+        // the chosen gates divided by their sum (the factor route_scale is in them already)
+        float* w = wgt + (size_t)t * top;
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += w[k];
+        const float inv = route_scale / (sum + 1e-20f * route_scale);
+        for (int k = 0; k < top; ++k) w[k] *= inv;
+    }
 }
 
 LLB_API int llb_moe_select(const float* z, int ldz, const float* bias, int T, int E, int top, float route_scale, int* idx,
-                           float* wgt, int mode, cudaStream_t stream) {
+                           float* wgt, int mode, int n_groups, int keep_groups, int renorm, cudaStream_t stream) {
     if (T == 0) return 0;
     if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
+    if (n_groups > 1 && (n_groups > 64 || E % n_groups || keep_groups < 1 || keep_groups > n_groups)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)4 * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    llb_launch(moe_select_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, z, ldz, bias, T, E, top, route_scale, idx, wgt, mode);
+    llb_launch(moe_select_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, z, ldz, bias, T, E, top, route_scale, idx, wgt, mode,
+               n_groups, keep_groups, renorm);
     return llb_status();
 }
 

@@ -24,40 +24,50 @@ class DecoderModel:
                 subs.append(SubLayer(sub.category, build_part(sub.category, sub.part, env), norm, post))
             self.blocks.append(part_class("block", ls.block)(subs, env, ls.params))
         # Every mixer of every entry of the run order is a user of the cache with an index of its own.
-        self.users: List[tuple] = []                 # user -> (order entry, layer, sub-layer index)
-        self.call_users: List[tuple] = []            # order entry -> its users, in sub-layer order
+        self.users: List[tuple] = []                 # user -> (order entry, layer, sub-layer index, index among the mixer's users)
+        self.call_users: List[tuple] = []            # order entry -> the first user of each of its mixers, in sub-layer order
+        self.call_all_users: List[tuple] = []        # order entry -> all its users
         for c, call in enumerate(spec.order):
             if not (0 <= call.layer < len(self.blocks)):
                 raise ValueError(f"run order entry {c} names layer {call.layer}, which does not exist")
-            mine = []
+            mine, all_mine = [], []
             for i, sub in enumerate(self.blocks[call.layer].sublayers):
                 if sub.category == "mixer":
                     mine.append(len(self.users))
-                    self.users.append((c, call.layer, i))
+                    for k in range(len(sub.part.cache_users())):
+                        all_mine.append(len(self.users))
+                        self.users.append((c, call.layer, i, k))
             self.call_users.append(tuple(mine))
+            self.call_all_users.append(tuple(all_mine))
+        self.reentry = build_part("reentry", spec.reentry, env) if spec.reentry is not None else None
+        if self.reentry is None and any(c.opens_pass is not None for c in spec.order):
+            raise ValueError("the run order opens passes but the model names no part for what a pass starts with")
         self.final_norm = build_part("norm", spec.final_norm, env)
         self.head = build_part("head", spec.head, env)
         self._loaded = False
 
     def _mixer(self, user: int):
-        _, layer, i = self.users[user]
+        _, layer, i, _ = self.users[user]
         return self.blocks[layer].sublayers[i].part
 
-    # ---- what the cache has to provide, per user (a mixer of an entry of the run order)
+    def _asks(self, user: int):
+        return self._mixer(user).cache_users()[self.users[user][3]]
+
+    # ---- what the cache has to provide, per user (a mixer of an entry of the run order, or one of its several kinds of rows)
     def kv_needs(self) -> List[Optional[KVNeed]]:
-        return [self._mixer(u).kv_need() for u in range(len(self.users))]
+        return [self._asks(u)[0] for u in range(len(self.users))]
 
     def cache_of(self) -> List[Optional[int]]:
         out: List[Optional[int]] = []
-        for u, (c, _, _) in enumerate(self.users):
+        for u, (c, _, _, _) in enumerate(self.users):
             owner = self.spec.order[c].cache_of
             if owner is None:
                 out.append(None)
                 continue
             if not (0 <= owner < c):
                 raise ValueError(f"run order entry {c} reads the cache of entry {owner}, which does not come before it")
-            k = self.call_users[c].index(u)
-            theirs = self.call_users[owner]
+            k = self.call_all_users[c].index(u)
+            theirs = self.call_all_users[owner]
             if k >= len(theirs):
                 raise ValueError(f"run order entry {c} reads the cache of entry {owner}, which has fewer mixers")
             out.append(theirs[k])
@@ -69,7 +79,7 @@ class DecoderModel:
         return int(f()) if f else 0
 
     def state_sizes(self) -> List[int]:
-        return [self._mixer(u).state_size() for u in range(len(self.users))]
+        return [self._asks(u)[1] for u in range(len(self.users))]
 
     def capturable(self) -> bool:
         """True when every part's forward only enqueues device work (no host read-back), so that
@@ -88,9 +98,17 @@ class DecoderModel:
             if b.spec is not None:                   # an arrangement with tensors of its own
                 ps.append(b)
             for sub in b.sublayers:
-                ps += ([sub.norm] if sub.norm is not None else []) + [sub.part]
+                ps += ([sub.norm] if sub.norm is not None else []) + [sub.part] + self._children(sub.part)
                 ps += [sub.post_norm] if sub.post_norm is not None else []
-        return ps + [self.final_norm, self.head]
+        return ps + ([self.reentry] if self.reentry is not None else []) + [self.final_norm, self.head]
+
+    @staticmethod
+    def _children(part) -> List[Part]:
+        """The parts a part is made of (a mixer of several mixers), at any depth; they own tensors of their own."""
+        out: List[Part] = []
+        for child in getattr(part, "children", lambda: [])():
+            out += [child] + DecoderModel._children(child)
+        return out
 
     def expected_tensors(self) -> Dict[str, TensorDecl]:
         out: Dict[str, TensorDecl] = {}
@@ -132,7 +150,10 @@ class DecoderModel:
             raise RuntimeError("the model has no weights yet")
         residual = self.embedding.forward(ctx)
         pending = None
+        first = self.reentry.remember(residual) if self.reentry is not None else None
         for c, call in enumerate(self.spec.order):
+            if call.opens_pass is not None:
+                residual, pending = self.reentry.forward(residual, pending, first, call.opens_pass)
             residual, pending = self.blocks[call.layer].forward(residual, pending, ctx, self.call_users[c])
         if ctx.out_rows.numel() == 0:
             return None

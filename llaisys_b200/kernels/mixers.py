@@ -15,20 +15,27 @@ from .ops import DT, KernelError, _AttnParams, _attn_lib, _check, _dt, _fn, _nee
 class _GlaParams(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("row_stride", c_int), ("z", c_void_p), ("z_stride", c_int),
                 ("state", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("out", c_void_p), ("H", c_int),
-                ("dk", c_int), ("dv", c_int), ("q_scale", c_float), ("inv_tau", c_float), ("z_is_decay", c_int)]
+                ("dk", c_int), ("dv", c_int), ("q_scale", c_float), ("inv_tau", c_float), ("z_is_decay", c_int),
+                ("head_decay", c_void_p), ("act", c_int)]
 
 
 GLA_MAX_KEY_DIM = 256
 
 
-def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor,
-             seq_slot: torch.Tensor, n_seqs: int, q_scale: float, decay_root: float) -> torch.Tensor:
+def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: Optional[torch.Tensor], state: torch.Tensor, seq_start: torch.Tensor,
+             seq_slot: torch.Tensor, n_seqs: int, q_scale: float, decay_root: float, head_decay: Optional[torch.Tensor] = None,
+             act: Optional[str] = None) -> torch.Tensor:
     """The gated-linear-attention recurrence over the new tokens of every sequence: proj [T, >= 2 H dk + H dv] holds the
     heads' queries, then keys, then values; z [T, H dk] (float32) the decay logits; state [slots, H dk dv] (float32) is
     read at row seq_slot[b] and left holding the state after the step.  Returns o [T, H dv] in float32.  For more than
-    64 tokens the decays are formed by a pass of their own over z (in place), once per token and channel."""
-    _need_cuda(proj, z, state)
-    assert z.dtype == torch.float32 and z.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    64 tokens the decays are formed by a pass of their own over z (in place), once per token and channel.
+    head_decay (float32 [H]) instead of z: one constant decay per head, S <- decay_h S + k v^T.  act "silu": q, k and v
+    pass through silu (in float32) on their way into the recurrence."""
+    _need_cuda(proj, z, state, head_decay)
+    assert (z is None) != (head_decay is None)
+    assert z is None or (z.dtype == torch.float32 and z.stride(1) == 1)
+    assert head_decay is None or (head_decay.dtype == torch.float32 and head_decay.numel() == H and head_decay.is_contiguous())
+    assert state.dtype == torch.float32 and state.is_contiguous()
     assert proj.stride(1) == 1 and state.shape[1] == H * dk * dv
     if dk > GLA_MAX_KEY_DIM:
         raise KernelError(f"gated linear attention: {dk} key channels a head; the kernel takes up to {GLA_MAX_KEY_DIM}")
@@ -37,10 +44,11 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, stat
     p = _GlaParams()
     es = proj.element_size()
     p.q, p.k, p.v = proj.data_ptr(), proj.data_ptr() + H * dk * es, proj.data_ptr() + 2 * H * dk * es
-    p.row_stride, p.z, p.z_stride = proj.stride(0), z.data_ptr(), z.stride(0)
+    p.row_stride, p.z, p.z_stride = proj.stride(0), _ptr(z), z.stride(0) if z is not None else 0
+    p.head_decay, p.act = _ptr(head_decay), {None: 0, "silu": 1}[act]
     p.state, p.seq_start, p.seq_slot, p.out = state.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(), out.data_ptr()
     p.H, p.dk, p.dv, p.q_scale, p.inv_tau = H, dk, dv, q_scale, 1.0 / decay_root
-    if T > 64 and z.is_contiguous():
+    if z is not None and T > 64 and z.is_contiguous():
         g = _fn(load_module("gla.cu"), "llb_gla_decay", [c_void_p, ctypes.c_longlong, c_float, c_void_p])
         _check(g(_ptr(z), z.numel(), 1.0 / decay_root, _stream()), "gated linear attention (decays)")
         p.z_is_decay = 1
@@ -50,7 +58,7 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, stat
 
 
 def gla_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, H: int, dv: int, eps: float,
-            out_dtype: torch.dtype) -> torch.Tensor:
+            out_dtype: torch.dtype, gate_act: str = "silu") -> torch.Tensor:
     """[T, H dv]: every head's o (float32) RMS-normed over its dv channels with `weight` [dv], times silu(gate) (gate a
     [T, H dv] view with any row stride, in the output's dtype)."""
     _need_cuda(o, gate, weight)
@@ -58,8 +66,9 @@ def gla_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, H: int, d
     assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == out_dtype and gate.stride(1) == 1
     out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
     f = _fn(load_module("gla.cu"), "llb_gla_out", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                                  c_int, c_float, c_void_p])
-    _check(f(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _dt(weight), _ptr(out), DT[out_dtype], T, H, dv, eps, _stream()),
+                                                  c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _dt(weight), _ptr(out), DT[out_dtype], T, H, dv, eps,
+             {"silu": 0, "sigmoid": 1}[gate_act], _stream()),
            "gated linear attention (head norm and gate)")
     return out
 

@@ -328,18 +328,20 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-GLU_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+GLU_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "swish_clamped": 3}
 
 
-def glu(gate_up: torch.Tensor, act: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def glu(gate_up: torch.Tensor, act: str, out_dtype: Optional[torch.dtype] = None, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """[T, 2I] (gate columns first) -> [T, I]: act(gate) * up with act "silu", "relu" or "gelu_tanh", in float32 with
-    one rounding at the output."""
+    one rounding at the output.  "swish_clamped": g = min(gate, limit), u = clamp(up, -limit, limit),
+    out = g sigmoid(alpha g) (u + 1)."""
     _need_cuda(gate_up)
     assert gate_up.is_contiguous()
     T, I2 = gate_up.shape
     out = torch.empty((T, I2 // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
-    f = _fn(_lib_basic(), "llb_glu", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _dt(out), _ptr(gate_up), _dt(gate_up), T, I2 // 2, GLU_ACTS[act], _stream()), f"gated activation ({act})")
+    f = _fn(_lib_basic(), "llb_glu", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_ptr(out), _dt(out), _ptr(gate_up), _dt(gate_up), T, I2 // 2, GLU_ACTS[act], float(limit), float(alpha), _stream()),
+           f"gated activation ({act})")
     return out
 
 
@@ -694,7 +696,9 @@ class _AttnParams(ctypes.Structure):
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p),
                 ("keep_first", c_int), ("pinned", c_int), ("sink", c_int),
                 ("sink_logits", c_void_p), ("v_in_k", c_int), ("kv_row_stride", c_int),
-                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int)]
+                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int),
+                ("chunk", c_int), ("maps", c_int), ("out_f32", c_int), ("pool", c_int), ("pool_k", c_void_p), ("pool_v", c_void_p),
+                ("pool_table", c_void_p), ("pool_table_stride", c_int)]
 
 
 class _MmaAttnParams(ctypes.Structure):
@@ -783,7 +787,14 @@ class AttnExtras:
     query position i and key position j loses r1[h] ln(1 + r2[h] (i - j)); a query temperature, `q_temp` = (coef, every):
     the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  The last two run on the mma.sync
     kernels (bfloat16, keys and values of one width that is a multiple of 16 up to 128) and on the CUDA-core kernel (every
-    other case, both precisions), not on the tcgen05 prefill kernel."""
+    other case, both precisions), not on the tcgen05 prefill kernel.
+
+    Four more, on the CUDA-core kernel only: `chunk` (the query at position p sees no key before floor(p / chunk) * chunk);
+    `maps` (that many key heads share one value head: `nkvh` counts key heads, query head h uses key head h / (nh / nkvh)
+    and value head (h / (nh / nkvh)) / maps, and a cache key row holds the maps' keys side by side); `out_f32` (the result
+    is float32 whatever the operands are); `pool` = (P, blocks): beside the keys of a window W, one key and value per block
+    of P positions that lies wholly before the window (block b is seen from position p when b P + P - 1 <= p - W), read
+    at row b of the cache view `blocks`; tokens and blocks share one softmax."""
     value_dim: Optional[int] = None
     keep_first: int = 0
     pinned: int = 0
@@ -791,10 +802,18 @@ class AttnExtras:
     sink_logits: Optional[torch.Tensor] = None
     dist_bias: Optional[tuple] = None
     q_temp: Optional[tuple] = None
+    chunk: int = 0
+    maps: int = 1
+    out_f32: bool = False
+    pool: Optional[tuple] = None
 
     def plain(self, dh: int) -> bool:
         return (self.value_dim in (None, dh) and not self.keep_first and not self.pinned and not self.sink
-                and self.sink_logits is None and not self.positional())
+                and self.sink_logits is None and not self.positional() and not self.cuda_core_only())
+
+    def cuda_core_only(self) -> bool:
+        """True with an option that only the CUDA-core kernel has."""
+        return bool(self.chunk) or self.maps > 1 or self.out_f32 or self.pool is not None
 
     def positional(self) -> bool:
         """True with an option that makes a score depend on the positions themselves."""
@@ -824,6 +843,17 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
                 p.q_temp_coef, p.q_temp_every = float(extras.q_temp[0]), int(extras.q_temp[1])
                 if p.q_temp_every <= 0:
                     raise KernelError("attention: the query temperature's period must be positive")
+        if extras.cuda_core_only():
+            if cls is not None and cls is not _AttnParams:
+                raise KernelError("attention: chunks, several score maps, pooled blocks and float32 results need the CUDA-core kernel")
+            p.chunk, p.maps, p.out_f32 = int(extras.chunk), int(extras.maps), int(extras.out_f32)
+            if extras.pool is not None:
+                P, blocks = extras.pool
+                if not window or P <= 0:
+                    raise KernelError("attention: pooled blocks lie before a window; there is none")
+                assert blocks.k.dtype == qkv.dtype and blocks.v is not None
+                p.pool, p.pool_k, p.pool_v = int(P), blocks.k.data_ptr(), blocks.v.data_ptr()
+                p.pool_table, p.pool_table_stride = blocks.page_table.data_ptr(), blocks.page_table.shape[1]
     p.row_stride = qkv.stride(0)
     p.out = out.data_ptr()
     p.kpool, p.vpool = kpool.data_ptr(), vpool.data_ptr()
@@ -937,15 +967,16 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
     """Attention with AttnExtras.  qkv holds nh query heads of dh, then (unless everything comes from the cache) nkvh key
     heads of dh and nkvh value heads of value_dim."""
     dv = extras.value_dim or dh
-    out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
-    if (not decode and dv == dh and all_from_cache and prefill_tc_ok(qkv.dtype, dh) and not extras.pinned and scale > 0
+    out = torch.empty((qkv.shape[0], nh * dv), dtype=torch.float32 if extras.out_f32 else qkv.dtype, device=qkv.device)
+    only_simt = extras.cuda_core_only()
+    if (not only_simt and not decode and dv == dh and all_from_cache and prefill_tc_ok(qkv.dtype, dh) and not extras.pinned and scale > 0
             and extras.sink_logits is None and not extras.positional()
             and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0):
         # a cache that keeps every key, head size 64 or 128: the tcgen05 prefill kernel, as for the plain attention
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
                               window, scale, 0, extras.keep_first, extras.sink)
         return out
-    if dv == dh and _mma_ok(qkv, dh):
+    if not only_simt and dv == dh and _mma_ok(qkv, dh):
         # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention
         # (a distance penalty and a query temperature are applied to the score fragments in registers)
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
@@ -1012,13 +1043,17 @@ MOE_GATES = {"sigmoid": 0, "softmax_chosen": 1}
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, route_scale: float,
-              gate: str = "sigmoid", n_experts: Optional[int] = None, with_logits: bool = False):
+              gate: str = "sigmoid", n_experts: Optional[int] = None, with_logits: bool = False, groups: Optional[tuple] = None,
+              renorm: bool = False):
     """(int32 [T, top] experts, float32 [T, top] weights): the router's logits x router^T in float32 (a matrix product
     with float32 accumulation: on the tensor cores for bfloat16 operands, on the CUDA cores in float32).  gate "sigmoid":
     gates sigmoid(logits); the `top` largest of gate + bias are chosen (first maximum first); a weight is
     gate * route_scale.  gate "softmax_chosen": the `top` largest logits (+ bias) are chosen and the weights are the softmax
     over the chosen logits alone, times route_scale.  n_experts: the router's matrix has further rows after the experts'
-    (other per-token logits that ride on the same product); with_logits also returns all logits [T, rows] (float32)."""
+    (other per-token logits that ride on the same product); with_logits also returns all logits [T, rows] (float32).
+    groups = (count, keep): the experts form `count` equal groups of neighbours, a group's score is the sum of its two
+    largest choice scores, and only experts of the `keep` best groups can be chosen.  renorm (gate "sigmoid"): the chosen
+    gates are divided by their sum (+ 1e-20) before route_scale is applied."""
     _need_cuda(x, router, bias)
     T, H = x.shape
     rows = router.shape[0]
@@ -1035,8 +1070,13 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
     z = linear(x, router, out_dtype=torch.float32, plan=plan)
     idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
-    _check(f(_ptr(z), z.stride(0), _ptr(bias), T, E, top, route_scale, _ptr(idx), _ptr(wgt), MOE_GATES[gate], _stream()), "router's choice")
+    n_groups, keep_groups = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+    if n_groups > 1 and (E % n_groups or not (1 <= keep_groups <= n_groups) or n_groups > 64):
+        raise KernelError(f"router: {E} experts in {n_groups} groups of which {keep_groups} are kept cannot be (equal groups, at most 64)")
+    f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int,
+                                           c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(bias), T, E, top, route_scale, _ptr(idx), _ptr(wgt), MOE_GATES[gate], n_groups, keep_groups,
+             int(renorm), _stream()), "router's choice")
     return (idx, wgt, z) if with_logits else (idx, wgt)
 
 

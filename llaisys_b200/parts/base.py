@@ -8,6 +8,7 @@ A model is put together from parts of five categories:
   position  position encoding applied by a mixer to its queries and keys
   block     the arrangement of a layer's sub-layers (a mixer or a feed-forward, each behind its
             norm) around the residual stream
+  reentry   what joins the stream where the run order starts another pass over a run of layers
 
 plus the token embedding and the output head.  Every part is built from a `PartSpec` (its sizes
 and constants) and a `BuildEnv` (activation dtype, device); it declares the tensors it wants by
@@ -25,7 +26,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head", "reentry")
 _REGISTRY: Dict[Tuple[str, str], type] = {}
 
 
@@ -85,12 +86,15 @@ class KVNeed:
     """What a mixer keeps per token: `num_kv_heads` rows of `key_dim` elements in the key pool and
     of `value_dim` elements in the value pool (value_dim 0: no value pool, e.g. one latent row
     per token).  `window` None keeps every token, else the last `window` and, for good, the first
-    `keep_first` tokens of the sequence."""
+    `keep_first` tokens of the sequence.  `every` > 1: the mixer keeps one row per block of `every` consecutive tokens
+    (row b belongs to the positions b * every .. b * every + every - 1 and exists once the last of them has arrived), so a
+    sequence of n tokens holds floor(n / every) rows."""
     num_kv_heads: int
     key_dim: int
     value_dim: int
     window: Optional[int] = None
     keep_first: int = 0
+    every: int = 1
 
 
 class Part:
@@ -151,6 +155,12 @@ class Mixer(Part):
     def state_size(self) -> int:
         """float32 elements of fixed-size state per sequence (zeroed when a sequence starts)."""
         return 0
+
+    def cache_users(self):
+        """[(KVNeed or None, state size)]: what this mixer asks of the cache, one entry per user.  A mixer is one user
+        unless it keeps several kinds of rows (tokens and blocks of tokens, say) or is made of several mixers; it then
+        gets consecutive user indices, the first of which is the `call` its forward() is handed."""
+        return [(self.kv_need(), self.state_size())]
 
     def forward(self, x: torch.Tensor, ctx, call: int) -> torch.Tensor:
         """x: normalised activations [T, H] of the step's packed tokens.  Returns what is to be

@@ -166,8 +166,75 @@ class DepthAveragedResidual(Block):
         return planes[self.index + 1], PendingDepthSum(residual, delta, self.mult, self.weights, x0, planes)
 
 
+@register_part("block", "gated_residual")
+class GatedResidual(Block):
+    """x -> x + sigmoid(Wg h + bg) * part(h), h = norm(x), for every sub-layer in turn: a part's result passes, element by
+    element, through a gate that is computed from the same normed input the part reads; every sub-layer has a gate matrix
+    [H, H] and bias [H] of its own.  The gate's logits leave their matrix product in float32.  The gated add and the norm
+    that follows are one pass over the row (kernels.stream_join); a layer's last part is left pending (PendingGated) for
+    whoever reads the stream next, so a layer costs one pass per sub-layer.  Needs RMS norms.
+
+    params: hidden_size, prefix, gates (the local names of the sub-layers' gate matrices, in order; a bias is the
+    matrix's name + ".b")."""
+    capturable = True
+
+    def __init__(self, sublayers, env, params=None):
+        super().__init__(sublayers, env, params)
+        p = self.params
+        self.hidden, self.gates = int(p["hidden_size"]), [str(g) for g in p["gates"]]
+        if len(self.gates) != len(self.sublayers):
+            raise ValueError(f"{len(self.sublayers)} sub-layers but {len(self.gates)} gates")
+        self.spec = PartSpec("gated_residual", p, prefix=str(p.get("prefix", "")))
+        for sub in self.sublayers:
+            if sub.norm is None or sub.norm.kind != "rms_norm":
+                raise ValueError("every sub-layer of this arrangement sits behind an RMS norm")
+        self.w, self.b = [], []
+
+    def tensors(self):
+        t = {}
+        for g in self.gates:
+            t[g] = TensorDecl((self.hidden, self.hidden))
+            t[g + ".b"] = TensorDecl((self.hidden,), use="vector")
+        return t
+
+    def load(self, tensors):
+        self.w = [tensors[g].contiguous() for g in self.gates]
+        self.b = [tensors[g + ".b"].float().contiguous() for g in self.gates]
+
+    def forward(self, residual, pending, ctx, users):
+        from .. import kernels
+        mixers = iter(users)
+        for i, sub in enumerate(self.sublayers):
+            h = settle(residual, pending, sub.norm)
+            gate = kernels.linear(h, self.w[i], self.b[i], out_dtype=torch.float32)
+            if sub.category == "mixer":
+                delta = sub.part.forward(h, ctx, next(mixers))
+            else:
+                delta = sub.part.forward(h, ctx)
+            pending = PendingGated(delta, gate)
+        return residual, pending
+
+
 class Deferred:
     """What a block may leave for whoever reads the stream next (the next block's first norm, or the output norm)."""
+
+
+class PendingGated(Deferred):
+    """A part's output that has not joined the stream yet: it joins as sigmoid(gate) * delta (gate: float32 logits, None:
+    as it is), together with `rows_add` (float32 [T, H]) and `vec_add` (float32 [H]) where given."""
+
+    def __init__(self, delta=None, gate=None, rows_add=None, vec_add=None):
+        self.delta, self.gate, self.rows_add, self.vec_add = delta, gate, rows_add, vec_add
+
+    def settle(self, residual, norm=None, rows=None):
+        from .. import kernels
+        fused = norm is not None and rows is None and norm.kind == "rms_norm" and norm.weight.dtype == torch.float32
+        h = kernels.stream_join(residual, self.delta, self.gate, rows_add=self.rows_add, vec_add=self.vec_add,
+                                weight=norm.weight if fused else None, eps=norm.eps if fused else 0.0,
+                                out_dtype=norm.env.dtype if fused else None)
+        if norm is None or fused:
+            return h
+        return norm.forward(residual, None, rows=rows)
 
 
 class PendingNormed(Deferred):
@@ -201,7 +268,7 @@ def settle(residual, pending, norm=None, rows=None):
     """Adds whatever the block before left pending to the float32 stream and returns `norm` of the result (None without
     a norm).  With `rows` only those rows are returned (the stream itself is still brought up to date)."""
     from .. import kernels
-    if isinstance(pending, PendingDepthSum):
+    if isinstance(pending, (PendingDepthSum, PendingGated)):
         return pending.settle(residual, norm, rows)
     if isinstance(pending, PendingNormed):
         if rows is None:

@@ -76,7 +76,7 @@ class LMHead(Part):
     """logits = h W^T in float32, no bias (xsmccc/llaisys src/models/qwen2/qwen2.cpp:76-77).
     With params["tied_to"] set, W is the tensor of that name (the embedding table) and the part
     declares no tensor of its own.  params: vocab_size, hidden_size, tied_to, tensor (the matrix's local name,
-    "weight" unless given)."""
+    "weight" unless given), scale (default 1: the float32 logits are multiplied by it)."""
     capturable = True
 
 
@@ -85,6 +85,7 @@ class LMHead(Part):
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.tied_to = spec.params.get("tied_to")
         self.tensor = str(spec.params.get("tensor", "weight"))
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensors(self):
@@ -99,4 +100,5 @@ class LMHead(Part):
 
     def forward(self, h):
         import torch
-        return kernels.linear(h, self.weight, out_dtype=torch.float32)
+        logits = kernels.linear(h, self.weight, out_dtype=torch.float32)
+        return kernels.scale_(logits, self.scale) if self.scale != 1.0 else logits

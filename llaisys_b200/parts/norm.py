@@ -10,7 +10,9 @@ class RMSNorm(Norm):
     (xsmccc/llaisys src/ops/rms_norm/cpu/rms_norm_cpu.cpp:15-34), fused with the residual add
     that precedes it (src/models/qwen2/layer.hpp:60-71).  params: size, eps, tensor (the weight's local name, "weight" unless
     given; "" when the tensor carries the part's own name), offset (default 0: with an offset c the stored tensor is
-    the weight's distance from c, y = x * (c + w) / ...; the sum is formed in float32 when the weights are loaded).
+    the weight's distance from c, y = x * (c + w) / ...; the sum is formed in float32 when the weights are loaded),
+    scalar (default false: true when the stored weight is a single number for all coordinates; it is kept as a float32
+    vector of `size` equal values).
 
     forward_scaled_add() is the same norm on a part's output on its way into the stream:
     residual += mult * norm(delta), and in the same pass the next norm of the new stream."""
@@ -22,13 +24,18 @@ class RMSNorm(Norm):
         self.size, self.eps = int(spec.params["size"]), float(spec.params["eps"])
         self.tensor = str(spec.params.get("tensor", "weight"))
         self.offset = float(spec.params.get("offset", 0.0))
+        self.scalar = bool(spec.params.get("scalar", False))
         self.weight = None
 
     def tensors(self):
-        return {self.tensor: TensorDecl((self.size,), init="normal" if self.offset else "one_plus_normal", use="vector")}
+        return {self.tensor: TensorDecl(() if self.scalar else (self.size,), init="normal" if self.offset else "one_plus_normal",
+                                        use="vector")}
 
     def load(self, tensors):
         w = tensors[self.tensor]
+        if self.scalar:
+            self.weight = (w.float().reshape(1) + self.offset).expand(self.size).contiguous()
+            return
         # a weight stored as a distance from the offset: the sum would lose the stored bits in 16-bit arithmetic
         self.weight = (w.float() + self.offset).contiguous() if self.offset else w.contiguous()
 

@@ -66,13 +66,13 @@ class RotaryHalfSplit(PositionEncoding):
                             tok_pos=ctx.tok_pos, err=ctx.err)
 
 
-def _leading_tables(dims: int, base: float, device, rows: int):
-    key = ("leading", dims, base, str(device))
+def _leading_tables(dims: int, base: float, device, rows: int, factor: float = 1.0):
+    key = ("leading", dims, base, str(device)) + ((factor,) if factor != 1.0 else ())
     have = _TABLES.get(key)
     if have is None or have[0].shape[0] < rows:
         half = dims // 2
         i = torch.arange(half, dtype=torch.float64)
-        freq = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * i / dims)
+        freq = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * i / dims) / factor
         ang = torch.arange(rows, dtype=torch.float64)[:, None] * freq[None, :]
         have = (torch.cos(ang).to(torch.float32).to(device).contiguous(), torch.sin(ang).to(torch.float32).to(device).contiguous())
         _TABLES[key] = have
@@ -86,13 +86,17 @@ class RotaryLeading(PositionEncoding):
     dimensions from `dims` on pass unchanged.  dims = head_dim is the half-split rotation of whole heads; dims = 0
     encodes nothing.  Tables [positions, dims/2] are built in float64 on the host and kept in float32, sized once by
     prepare().  Mixers that rotate in their own kernels take the tables through pair_tables(); `pair_layout` tells them
-    which dimensions pair up.  params: head_dim, dims, base."""
+    which dimensions pair up.  params: head_dim, dims, base, factor (default 1: every frequency is divided by it, the
+    linear stretching of positions)."""
     capturable = True
     pair_layout = "halves"
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.head_dim, self.dims, self.base = int(spec.params["head_dim"]), int(spec.params["dims"]), float(spec.params["base"])
+        self.factor = float(spec.params.get("factor", 1.0))
+        if self.factor <= 0:
+            raise ValueError(f"the frequencies' divisor must be positive, got {self.factor}")
         if self.dims % 2 or not (0 <= self.dims <= self.head_dim):
             raise ValueError(f"rotated dimensions must be even and at most the head size {self.head_dim}, got {self.dims}")
         self._tables = None
@@ -107,7 +111,7 @@ class RotaryLeading(PositionEncoding):
                 raise ValueError(f"position {positions - 1} lies beyond the {self._tables[0].shape[0]} positions the "
                                  f"rotary table was prepared for")
             rows = max(positions, 2 * (self._tables[0].shape[0] if self._tables is not None else 0))
-            self._tables = _leading_tables(self.dims, self.base, self.env.device, rows)
+            self._tables = _leading_tables(self.dims, self.base, self.env.device, rows, self.factor)
         return self._tables
 
     def prepare(self, max_positions):
@@ -159,7 +163,8 @@ class RotaryInterleaved(PositionEncoding):
     rotated by the angle p * f_i at position p, (u, v) -> (u cos - v sin, v cos + u sin); the elements from `dims` on
     pass unchanged.  Frequencies and magnitude come from yarn_frequencies().  The part hands out float32 tables
     [positions, dims / 2] of cos and sin (magnitude included), built in float64 on the host and sized once by
-    prepare(); the mixers' kernels apply them.  params: width, dims, base, yarn (dict or None)."""
+    prepare(); the mixers' kernels apply them.  params: width, dims, base, yarn (dict or None), factor (default 1: every
+    frequency is divided by it, the linear stretching of positions)."""
     capturable = True
     pair_layout = "neighbours"
 
@@ -168,6 +173,9 @@ class RotaryInterleaved(PositionEncoding):
         p = spec.params
         self.width, self.dims, self.base = int(p["width"]), int(p["dims"]), float(p["base"])
         self.yarn = dict(p["yarn"]) if p.get("yarn") else None
+        self.factor = float(p.get("factor", 1.0))
+        if self.factor <= 0:
+            raise ValueError(f"the frequencies' divisor must be positive, got {self.factor}")
         if self.dims % 2 or not (0 <= self.dims <= self.width):
             raise ValueError(f"rotated dimensions must be even and at most {self.width}, got {self.dims}")
         self._tables = None
@@ -183,9 +191,12 @@ class RotaryInterleaved(PositionEncoding):
                                  f"rotary table was prepared for")
             rows = max(positions, 2 * (self._tables[0].shape[0] if self._tables is not None else 0))
             key = ("pairs", self.dims, self.base, tuple(sorted(self.yarn.items())) if self.yarn else None, str(self.env.device))
+            if self.factor != 1.0:
+                key += (self.factor,)
             have = _TABLES.get(key)
             if have is None or have[0].shape[0] < rows:
                 f, mag = yarn_frequencies(self.dims, self.base, self.yarn)
+                f = f / self.factor
                 ang = torch.arange(rows, dtype=torch.float64)[:, None] * f[None, :]
                 have = ((torch.cos(ang) * mag).to(torch.float32).to(self.env.device).contiguous(),
                         (torch.sin(ang) * mag).to(torch.float32).to(self.env.device).contiguous())
