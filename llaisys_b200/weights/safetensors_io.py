@@ -122,5 +122,5 @@ def write_safetensors(path, tensors, metadata: dict | None = None):
                 del made
             c = t.detach().to("cpu").contiguous()
             if c.numel():
-                f.write(c.view(torch.uint8).numpy().data)
+                f.write(c.reshape(-1).view(torch.uint8).numpy().data)     # (a single number has no axis to view by bytes)
             del c, t
