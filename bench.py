@@ -582,13 +582,42 @@ def zedirax_configs(size: str, layers: int):
     return zx, nubedra_configs(size, layers)[0]
 
 
+def zetalorn_configs(size: str, layers: int):
+    """(Zetalorn config, Vumezen config) of one size: the same width, heads, head size, window and routed experts as the
+    Vumezen model of that size (without its shared expert: this design has none).  Layers in turn: a parallel one
+    (window of that size with pooled blocks of 64 tokens, beside a constant-decay linear attention of half as many heads
+    with 64 key channels) and one with two score maps (half as many heads of twice the value width, chunks as long as
+    the window), every one with gated residuals and routed experts in 8 groups of which 4 are kept.  With six layers
+    or more, two of the layers run twice, so that the model has `layers` layer runs from `layers` - 2 layers."""
+    D, H, G, dh, rot, window, _, E, top, ff, _ = DESIGN_SIZES[size]
+    vocab = 32768
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top, "groups": {"count": 8, "keep": 4}}, "expert": {"ff": ff, "limit": 7.0}}
+    lh = max(1, H // 2)
+    kinds = [
+        {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": H, "kv_heads": G, "dim": dh, "vdim": dh, "scale": dh ** -0.5, "mask": {"size": window, "pool": 64},
+                     "rot": {"dims": rot, "base": 1000000.0}},
+            "right": {"heads": lh, "dim": 64, "vdim": dh, "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(1, lh - 1)) for i in range(lh)]}}},
+        {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": H // 2, "kv_heads": max(1, G // 2), "dim": dh, "vdim": 2 * dh, "scale": dh ** -0.5, "diff": 0.3,
+            "mask": {"size": window}, "rot": {"dims": rot, "base": 1000000.0, "scaling": {"factor": 4.0}}}},
+    ]
+    looped = layers >= 6
+    n = layers - 2 if looped else layers
+    zl = {"architecture": "Zetalorn", "vocab": vocab, "width": D, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+          "layers": [kinds[i % 2] for i in range(n)]}
+    if looped:
+        zl["loop"] = {"start": 2, "stop": 4, "times": 2}
+    return zl, design_configs(size, layers)[0]
+
+
 DESIGNS = {"vumezen": (DESIGN_SIZES, design_configs, "qwen2"), "nubedra": (NUBEDRA_SIZES, nubedra_configs, "qwen2"),
-           "zedirax": (NUBEDRA_SIZES, zedirax_configs, "nubedra")}
+           "zedirax": (NUBEDRA_SIZES, zedirax_configs, "nubedra"), "zetalorn": (DESIGN_SIZES, zetalorn_configs, "vumezen")}
 
 
 def design_run(args) -> int:
     """Prefill (one step over --tokens tokens) and decode (--batch sequences that hold --tokens tokens each) of the
-    chosen design and of the model beside it (the Qwen2 dense decoder; for zedirax the Nubedra design) at equal layer sizes: time per step, tokens a second, and each kernel's
+    chosen design and of the model beside it (the Qwen2 dense decoder; for zedirax the Nubedra design, for zetalorn the Vumezen design) at equal layer sizes: time per step, tokens a second, and each kernel's
     share of a step (torch.profiler).  One JSON line per model and phase.  Inputs: the weights of either model are
     larger than L2, and nothing is flushed between steps."""
     import collections
@@ -823,7 +852,7 @@ def main() -> int:
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
-                    help="measure this design beside the Qwen2 dense decoder (zedirax: beside the Nubedra design) at equal layer sizes "
+                    help="measure this design beside the Qwen2 dense decoder (zedirax: beside the Nubedra design; zetalorn: beside the Vumezen design) at equal layer sizes "
                          "(prefill of --tokens tokens, decode at --batch) instead of the benchmark; --size picks among the sizes "
                          "(default: all)")
     ap.add_argument("--size", default=None, help="with --design: comma-separated sizes of " + ", ".join(sorted(DESIGN_SIZES)))
