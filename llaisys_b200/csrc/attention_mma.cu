@@ -80,6 +80,18 @@ struct MmaAttnParams {
     const float* dist_r2;   //   dist_r1[head] * ln(1 + dist_r2[head] * (i - j))
     float q_temp_coef;      // with q_temp_every > 0: the query at position p is multiplied by
     int q_temp_every;       //   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)
+    // prefill only:
+    int chunk;              // > 0: the query at position p sees no key before floor(p / chunk) * chunk
+    int maps;               // > 1: `maps` key heads share one value head; nkvh counts key heads, the cache has nkvh / maps
+                            //      heads whose key rows hold the maps' keys side by side
+    int out_f32;            // out is float32
+    int v_split;            // > 1: values (and outputs) are v_split * DH wide; a block owns one DH-wide part of them
+    int pool;               // > 0 (with a window): one key and value per block of `pool` positions that lies wholly before
+                            //      the window, at row b of a second cache; tokens and blocks share one softmax
+    const bf16* pool_k;
+    const bf16* pool_v;
+    const int* pool_table;  // [B, pool_table_stride]
+    int pool_table_stride;
 };
 
 // What a thread's two score rows need beyond the common scale when scores depend on the positions themselves: the
@@ -132,6 +144,9 @@ struct Source {
     int ring, nkvh, kvh, row_stride, tok0, len_before;
     bool use_new;           // positions >= len_before come from k_new / v_new
     int pinned = 0, keep = 0;
+    // heads of the cache (0: nkvh), the value head (-1: kvh), elements of a cache key row and the key's offset in it,
+    // elements of a value row and the offset of the part this block owns
+    int cache_heads = 0, vh = -1, krow = DH, koff = 0, vrow = DH, voff = 0;
     // a tile's first fetched key: a tile that holds kept first keys is fetched from its start
     __device__ __forceinline__ int lo_of(int tile, int key_lo) const { return tile * TILE < keep ? tile * TILE : key_lo; }
     // the combined walk: n_kept tiles of kept keys that lie before the window's first tile, then the window's tiles
@@ -144,20 +159,22 @@ __device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo
     constexpr int CH = ROW_BYTES / 16;                     // 16-byte chunks of a row
     const int p0 = tile * TILE;
     const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);       // valid rows [j_lo, j_hi)
-    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH, s.pinned);      // one page per tile
+    const int ch = s.cache_heads ? s.cache_heads : s.nkvh, vh = s.vh >= 0 ? s.vh : s.kvh;
+    const bool cached = !s.use_new || p0 < s.len_before;     // (a step without history may come with an empty table)
+    const size_t k_off = cached ? paged_row(s.table, s.ring, p0, vh, ch, s.krow, s.pinned) + s.koff : 0;      // one page per tile
+    const size_t v_off = cached ? paged_row(s.table, s.ring, p0, vh, ch, s.vrow, s.pinned) + s.voff : 0;
     for (int i = tid; i < TILE * CH; i += THREADS) {
         int j = i / CH, c = i - j * CH;
         if (j < j_lo || j >= j_hi) continue;
         int pos = p0 + j;
         const bf16 *ks, *vs;
         if (s.use_new && pos >= s.len_before) {
-            size_t off = (size_t)(s.tok0 + pos - s.len_before) * s.row_stride + (size_t)s.kvh * DH;
-            ks = s.k_new + off;
-            vs = s.v_new + off;
+            size_t off = (size_t)(s.tok0 + pos - s.len_before) * s.row_stride;
+            ks = s.k_new + off + (size_t)s.kvh * DH;
+            vs = s.v_new + off + (size_t)vh * s.vrow + s.voff;
         } else {
-            size_t off = page_off + (size_t)j * DH;
-            ks = s.kpool + off;
-            vs = s.vpool + off;
+            ks = s.kpool + k_off + (size_t)j * s.krow;
+            vs = s.vpool + v_off + (size_t)j * s.vrow;
         }
         uint32_t d = stage + j * ROW_STRIDE + c * 16;
         cp_async16(d, ks + c * 8);
@@ -778,13 +795,17 @@ __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __r
 }
 
 // ------------------------------------------------------------------ prefill
-template <bool BIAS>
+// EXT: chunks, several score maps, pooled blocks, split values and float32 results (compiled out otherwise, so that the
+// plain kernel is what it was without them)
+template <bool BIAS, bool EXT>
 __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnParams p) {
+    const int x_chunk = EXT ? p.chunk : 0, x_pool = EXT ? p.pool : 0, x_out_f32 = EXT ? p.out_f32 : 0;
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // Heads along x, row blocks along y with the last (longest) ones first: blocks are handed out x first, so the
     // long blocks of every head start first and the short ones fill the end of the launch.
-    const int b = blockIdx.z, head = blockIdx.x;
+    const int v_split = (EXT && p.v_split > 1) ? p.v_split : 1, maps = (EXT && p.maps > 1) ? p.maps : 1;
+    const int b = blockIdx.z, head = blockIdx.x / v_split, vpart = blockIdx.x - head * v_split;
     llb_grid_dependency_sync();
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
     const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * 64;
@@ -793,19 +814,37 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     const int kvh = head / (p.nh / p.nkvh);
     const int n_rows = min(64, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
-    const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+    auto lo_of_row = [&](int pos) {          // the first key position the query at `pos` sees (kept first keys aside)
+        int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        return x_chunk > 0 ? max(lo, (pos / x_chunk) * x_chunk) : lo;
+    };
+    auto blocks_seen = [&](int pos) { return (x_pool > 0 && p.window > 0) ? max(0, (pos - p.window + 1) / x_pool) : 0; };
+    const int key_lo = lo_of_row(first_pos);
+    const int blocks_hi = blocks_seen(last_pos), n_pool = (blocks_hi + TILE - 1) / TILE;    // pooled tiles, walked first
     // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's tiles
     const int keep = p.window > 0 ? p.keep_first : 0;
     const int tile_lo = key_lo / TILE, n_kept = min((keep + TILE - 1) / TILE, tile_lo);
-    const int n_tiles = n_kept + last_pos / TILE + 1 - tile_lo;
+    const int n_tiles = n_pool + n_kept + last_pos / TILE + 1 - tile_lo;
 #define PTILE(i) Source::tile_at(i, n_kept, tile_lo)
     // a tile of kept keys alone is fetched, and seen by every row, up to the last kept key
 #define PTILE_HI(i) ((i) < n_kept ? keep - 1 : last_pos)
 
     Source src{p.kpool, p.vpool, p.k_new, p.v_new, p.page_table + (size_t)b * p.table_stride,
-               p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache, p.pinned, keep};
+               p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache, p.pinned, keep,
+               p.nkvh / maps, kvh / maps, DH * maps, (kvh % maps) * DH, DH * v_split, vpart * DH};
+    Source blocks = src;                     // the cache of pooled blocks: "position" b is block b; nothing of it is in the step
+    blocks.kpool = p.pool_k;
+    blocks.vpool = p.pool_v;
+    blocks.table = p.pool_table + (size_t)b * p.pool_table_stride;
+    blocks.ring = p.pool_table_stride;
+    blocks.use_new = false;
+    blocks.pinned = blocks.keep = 0;
+    auto issue = [&](int i) {
+        if (i < n_pool) issue_tile(blocks, i, 0, blocks_hi - 1, ring.stage(i), tid);
+        else issue_tile(src, PTILE(i - n_pool), src.lo_of(PTILE(i - n_pool), key_lo), PTILE_HI(i - n_pool), ring.stage(i), tid);
+    };
     for (int i = 0; i < STAGES_PREFILL; ++i) {
-        if (i < n_tiles) issue_tile(src, PTILE(i), src.lo_of(PTILE(i), key_lo), PTILE_HI(i), ring.stage(i), tid);
+        if (i < n_tiles) issue(i);
         cp_async_commit();
     }
 
@@ -816,9 +855,9 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
         int row = warp * 16 + r;
         return row < n_rows ? p.q + (size_t)(tok0 + t0 + row) * p.row_stride + (size_t)head * DH : nullptr; }, lane);
     const int hi0 = first_pos + r0, hi1 = first_pos + r1;          // causal: keys up to the row's own position
-    const int lo0 = p.window > 0 ? max(0, hi0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, hi1 - p.window + 1) : 0;
+    const int lo0 = lo_of_row(hi0), lo1 = lo_of_row(hi1);
     const int warp_hi = first_pos + warp * 16 + 15;                  // last position any row of this warp sees
-    const int warp_lo = p.window > 0 ? max(0, first_pos + warp * 16 - p.window + 1) : 0;
+    const int warp_lo = lo_of_row(first_pos + warp * 16);
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     if (p.sink || p.sink_logits) {                                   // the sink's term (m is on the base-2 scale)
         m[0] = m[1] = p.sink_logits ? p.sink_logits[head] * 1.4426950408889634f : 0.f;
@@ -840,39 +879,52 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES_PREFILL - 1>();
         __syncthreads();
-        const int tile = PTILE(i), p0 = tile * TILE;
-        zero_unfetched(ring.stage_ptr(i), tile, src.lo_of(tile, key_lo), PTILE_HI(i), tid);
-        if (i < n_kept) {
+        if (i < n_pool) {
+            // pooled blocks i * TILE ..: row r sees the blocks below blocks_seen(its position)
+            zero_unfetched(ring.stage_ptr(i), i, 0, blocks_hi - 1, tid);
+            if (i * TILE < blocks_seen(warp_hi))
+                tile_step<8, true, false>(qf, o, m, l, ring.stage(i), 0, i * TILE, 0, blocks_seen(hi0) - 1, 0, blocks_seen(hi1) - 1,
+                                          scale_log2, lane, 0, rb);
+            __syncthreads();
+            if (i + STAGES_PREFILL < n_tiles) issue(i + STAGES_PREFILL);
+            cp_async_commit();
+            continue;
+        }
+        const int tile = PTILE(i - n_pool), p0 = tile * TILE;
+        zero_unfetched(ring.stage_ptr(i), tile, src.lo_of(tile, key_lo), PTILE_HI(i - n_pool), tid);
+        if (i - n_pool < n_kept) {
             // kept keys that lie before every row's window: all rows see the keys below `keep` and nothing else here
             tile_step<8, true, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, 0, keep - 1, 0, keep - 1, scale_log2, lane, 0, rb);
         } else if (p0 <= warp_hi && (p0 + TILE - 1 >= warp_lo || p0 < keep)) {   // the tile holds a key some row of the warp sees
             // every key of the tile visible to every row of the warp (most tiles of a causal prompt): no masks
-            const bool all_visible = p0 + TILE - 1 <= first_pos + warp * 16 &&
-                                     (p.window <= 0 || p0 >= first_pos + warp * 16 + 15 - p.window + 1);
+            const bool all_visible = p0 + TILE - 1 <= first_pos + warp * 16 && p0 >= lo_of_row(warp_hi);
             if (all_visible) tile_step<8, false, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, 0, rb);
             else tile_step<8, true, BIAS>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, keep, rb);
         }
         __syncthreads();
-        if (i + STAGES_PREFILL < n_tiles)
-            issue_tile(src, PTILE(i + STAGES_PREFILL), src.lo_of(PTILE(i + STAGES_PREFILL), key_lo), PTILE_HI(i + STAGES_PREFILL),
-                       ring.stage(i + STAGES_PREFILL), tid);
+        if (i + STAGES_PREFILL < n_tiles) issue(i + STAGES_PREFILL);
         cp_async_commit();
     }
 #undef PTILE
 #undef PTILE_HI
     cp_async_wait<0>();
     const int c = (lane & 3) * 2;
-    if (r0 < n_rows) {
-        float inv = 1.0f / l[0];
-        bf16* dst = p.out + (size_t)(tok0 + t0 + r0) * p.nh * DH + (size_t)head * DH + c;
+    const int vrow = DH * v_split;
 #pragma unroll
-        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][0] * inv, o[d][1] * inv);
-    }
-    if (r1 < n_rows) {
-        float inv = 1.0f / l[1];
-        bf16* dst = p.out + (size_t)(tok0 + t0 + r1) * p.nh * DH + (size_t)head * DH + c;
+    for (int half = 0; half < 2; ++half) {
+        const int r = half ? r1 : r0;
+        if (r >= n_rows) continue;
+        const float inv = 1.0f / l[half];
+        const size_t at = (size_t)(tok0 + t0 + r) * p.nh * vrow + (size_t)head * vrow + vpart * DH + c;
+        if (x_out_f32) {
+            float* dst = reinterpret_cast<float*>(p.out) + at;
 #pragma unroll
-        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][2] * inv, o[d][3] * inv);
+            for (int d = 0; d < DTILES; ++d) *reinterpret_cast<float2*>(dst + d * 8) = make_float2(o[d][2 * half] * inv, o[d][2 * half + 1] * inv);
+        } else {
+            bf16* dst = p.out + at;
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][2 * half] * inv, o[d][2 * half + 1] * inv);
+        }
     }
 }
 
@@ -897,19 +949,27 @@ bool aligned_ok(const MmaAttnParams& p) {
 LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream_t stream) {
     if (B == 0 || max_new == 0) return 0;
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
-    dim3 grid(p.nh, (max_new + 63) / 64, B);
+    if ((p.maps > 1 && p.nkvh % p.maps) || (p.pool > 0 && (!p.pool_k || !p.pool_v || !p.pool_table || p.window <= 0))) return (int)cudaErrorInvalidValue;
+    if (p.pool > 0 && (p.dist_r1 || p.q_temp_every > 0 || p.keep_first > 0 || (((uintptr_t)p.pool_k | (uintptr_t)p.pool_v) & 15)))
+        return (int)cudaErrorInvalidValue;
+    dim3 grid(p.nh * (p.v_split > 1 ? p.v_split : 1), (max_new + 63) / 64, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    const bool ext = p.chunk > 0 || p.maps > 1 || p.v_split > 1 || p.pool > 0 || p.out_f32;
+#define LLB_PREFILL(W, BIAS, EXT)                                                                                       \
+    do {                                                                                                                \
+        int rc = configure<W>(attn_mma_prefill_kernel<BIAS, EXT>, smem_bytes(STAGES_PREFILL));                          \
+        if (rc) return rc;                                                                                              \
+        llb_launch(attn_mma_prefill_kernel<BIAS, EXT>, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);     \
+        return llb_status();                                                                                            \
+    } while (0)
     if (p.dist_r1 || p.dist_r2 || p.q_temp_every > 0) {          // scores that depend on the positions themselves
         if (!p.dist_r1 != !p.dist_r2) return (int)cudaErrorInvalidValue;
-        int rc = configure<2>(attn_mma_prefill_kernel<true>, smem_bytes(STAGES_PREFILL));
-        if (rc) return rc;
-        llb_launch(attn_mma_prefill_kernel<true>, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
-        return llb_status();
+        if (ext) LLB_PREFILL(4, true, true);
+        LLB_PREFILL(2, true, false);
     }
-    int rc = configure<0>(attn_mma_prefill_kernel<false>, smem_bytes(STAGES_PREFILL));
-    if (rc) return rc;
-    llb_launch(attn_mma_prefill_kernel<false>, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
-    return llb_status();
+    if (ext) LLB_PREFILL(5, false, true);
+    LLB_PREFILL(0, false, false);
+#undef LLB_PREFILL
 }
 
 // How many clusters of `size` blocks of the decode kernel the device can hold at once (0: that size cannot be launched).

@@ -710,7 +710,9 @@ class _MmaAttnParams(ctypes.Structure):
                 ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
                 ("append_new", c_int), ("cluster", c_int), ("err", c_void_p),
                 ("keep_first", c_int), ("pinned", c_int), ("sink", c_int), ("sink_logits", c_void_p),
-                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int)]
+                ("dist_r1", c_void_p), ("dist_r2", c_void_p), ("q_temp_coef", c_float), ("q_temp_every", c_int),
+                ("chunk", c_int), ("maps", c_int), ("out_f32", c_int), ("v_split", c_int), ("pool", c_int), ("pool_k", c_void_p),
+                ("pool_v", c_void_p), ("pool_table", c_void_p), ("pool_table_stride", c_int)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -789,7 +791,8 @@ class AttnExtras:
     kernels (bfloat16, keys and values of one width that is a multiple of 16 up to 128) and on the CUDA-core kernel (every
     other case, both precisions), not on the tcgen05 prefill kernel.
 
-    Four more, on the CUDA-core kernel only: `chunk` (the query at position p sees no key before floor(p / chunk) * chunk);
+    Four more, on the CUDA-core kernel (both precisions, prompts and single tokens) and, for prompts in bfloat16 with keys
+    of a multiple of 16 up to 128 elements and values as wide or twice as wide, on the mma.sync prefill kernel: `chunk` (the query at position p sees no key before floor(p / chunk) * chunk);
     `maps` (that many key heads share one value head: `nkvh` counts key heads, query head h uses key head h / (nh / nkvh)
     and value head (h / (nh / nkvh)) / maps, and a cache key row holds the maps' keys side by side); `out_f32` (the result
     is float32 whatever the operands are); `pool` = (P, blocks): beside the keys of a window W, one key and value per block
@@ -812,7 +815,7 @@ class AttnExtras:
                 and self.sink_logits is None and not self.positional() and not self.cuda_core_only())
 
     def cuda_core_only(self) -> bool:
-        """True with an option that only the CUDA-core kernel has."""
+        """True with an option that only the CUDA-core kernel (and the mma.sync prefill kernel) has."""
         return bool(self.chunk) or self.maps > 1 or self.out_f32 or self.pool is not None
 
     def positional(self) -> bool:
@@ -844,8 +847,8 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
                 if p.q_temp_every <= 0:
                     raise KernelError("attention: the query temperature's period must be positive")
         if extras.cuda_core_only():
-            if cls is not None and cls is not _AttnParams:
-                raise KernelError("attention: chunks, several score maps, pooled blocks and float32 results need the CUDA-core kernel")
+            if cls is not None and cls not in (_AttnParams, _MmaAttnParams):
+                raise KernelError("attention: chunks, several score maps, pooled blocks and float32 results need the CUDA-core or the mma.sync kernel")
             p.chunk, p.maps, p.out_f32 = int(extras.chunk), int(extras.maps), int(extras.out_f32)
             if extras.pool is not None:
                 P, blocks = extras.pool
@@ -975,6 +978,17 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
         # a cache that keeps every key, head size 64 or 128: the tcgen05 prefill kernel, as for the plain attention
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
                               window, scale, 0, extras.keep_first, extras.sink)
+        return out
+    if (only_simt and not decode and dv in (dh, 2 * dh) and _mma_ok(qkv, dh) and not extras.keep_first and not extras.sink
+            and extras.sink_logits is None and (extras.pool is None or not extras.positional())
+            and not ((kpool.data_ptr() | vpool.data_ptr() | out.data_ptr()) & 15)):
+        # prompts in bfloat16: the mma.sync prefill kernel with its extensions (a block owns one half of values twice as
+        # wide as the keys, and repeats the scores for it)
+        p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
+                         _MmaAttnParams, extras=extras)
+        p.all_from_cache, p.v_split = int(all_from_cache), dv // dh
+        f = _fn(_mma_lib(dh), "llb_attn_mma_prefill", [_MmaAttnParams, c_int, c_int, c_void_p])
+        _check(f(p, n_seqs, max_new, _stream()), "attention_prefill (tensor cores)")
         return out
     if not only_simt and dv == dh and _mma_ok(qkv, dh):
         # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention

@@ -234,6 +234,38 @@ def test_two_score_maps_over_chunks_alone_at_every_edge(tmp_path, chunk, heads):
         compare(run_chunked(engine, toks, cuts), oracle, toks, torch.float32, like, f"portions {cuts}")
 
 
+@pytest.mark.parametrize("layer", [
+    zh.parallel((4, 2, 64, 64, 70, 8, zh.rot(32, 1000.0)), (1, 8, 8, (0.9,))),
+    zh.parallel((2, 2, 16, 32, 130, 3, zh.rot(16, 1000.0)), (1, 8, 8, (0.9,))),
+    zh.parallel((2, 1, 128, 128, 20, 64, None), (1, 8, 8, (0.9,))),
+    zh.attention(4, 2, 32, 64, 100, rotation=zh.rot(32, 500.0, 2.0)),
+    zh.attention(2, 1, 16, 16, 64, rotation=zh.rot(8, 500.0)),
+    zh.attention(3, 3, 64, 64, 1000, diff=0.1),
+], ids=["window70", "values_twice_as_wide", "head128", "maps_values_twice_as_wide", "maps16", "maps64"])
+def test_prompts_on_the_tensor_cores_against_the_cuda_core_kernel(tmp_path, layer, monkeypatch):
+    """bfloat16 prompts and portions with chunks, two score maps, pooled blocks and values twice as wide as the keys run on
+    the mma.sync prefill kernel; the same steps with that kernel switched off run on the CUDA-core one.  Both against
+    the plain implementation, and against each other row by row."""
+    from llaisys_b200.kernels import ops
+    cfg = zh.config(90, 64, [layer])
+    edit = _silence("l0.mix.right.o") if layer["type"] == "parallel" else None
+    folder = zh.make_folder(tmp_path, cfg, seed=3, gain=3.0, edit=edit)
+    oracle = zh.Oracle(folder)
+    toks = zh.random_requests(cfg, [300, 77], seed=5)
+    got = {}
+    for on in (True, False):
+        monkeypatch.setattr(ops, "MMA_ATTENTION", on)
+        engine = build_engine(folder, torch.bfloat16, max_tokens=448, max_seqs=2)
+        n0 = ops.launch_count()
+        got[on] = (run_whole(engine, toks), run_chunked(engine, toks, [130, 70, 1000]), run_batches(engine, toks, [[0, 1]], [250, 70]))
+        for g, what in zip(got[on], ("whole", "portions", "together")):
+            compare_zl(g, oracle, toks, torch.bfloat16, cfg, f"{what}, tensor cores {on}")
+    for a, b in zip(got[True], got[False]):
+        for key, ref in b.items():
+            rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
+            assert np.sqrt(((a[key] - ref).astype(np.float64) ** 2).mean()) <= 0.05 * rms + 1e-3, key
+
+
 def _one_direction(cfg, special, gain):
     """Embeddings that share one direction (negative along the first axis, little else), the special token alone on the
     other side of it; queries that ask for that side only, keys that are the stream's leading elements: the special token's
