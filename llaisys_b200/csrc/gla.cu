@@ -234,6 +234,42 @@ LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, int sms, cudaStream_t st
     return 0;
 }
 
+// ------------------------------------------------------------------ long steps with a constant decay per head, chunk by chunk
+// With one decay a_h per head the state after a run of n tokens is a_h^n S_before + (the state the run reaches from zero), so a
+// long step is cut into chunks that run side by side: the recurrence over every chunk from a zero state (its local state),
+// this kernel, and the recurrence again over every chunk from the state it really starts with.  Here, per sequence and state
+// element: carry = the sequence's state; for each of its chunks in order, tmp[chunk] (the local state) is replaced by carry
+// (what the chunk starts with) and carry <- a_h^len carry + local; at the end the sequence's state is carry.
+__global__ void __launch_bounds__(256)
+gla_chunk_prefix_kernel(float* __restrict__ tmp, float* __restrict__ state, const int* __restrict__ seq_chunk0,
+                        const int* __restrict__ chunk_len, const int* __restrict__ seq_slot, const float* __restrict__ head_decay,
+                        int per_head, int n_state) {
+    llb_grid_dependency_sync();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (e >= n_state) return;
+    const float a = head_decay[e / per_head];
+    float* st = state + (size_t)seq_slot[b] * n_state + e;
+    float carry = *st;
+    for (int c = seq_chunk0[b]; c < seq_chunk0[b + 1]; ++c) {
+        float* t = tmp + (size_t)c * n_state + e;
+        const float local = *t;
+        *t = carry;
+        float f = 1.f;
+        for (int i = 0; i < chunk_len[c]; ++i) f *= a;
+        carry = fmaf(f, carry, local);
+    }
+    *st = carry;
+}
+
+LLB_API int llb_gla_chunk_prefix(float* tmp, float* state, const int* seq_chunk0, const int* chunk_len, const int* seq_slot,
+                                 const float* head_decay, int per_head, int n_state, int B, cudaStream_t stream) {
+    if (B == 0 || n_state == 0) return 0;
+    if (B > 65535) return (int)cudaErrorInvalidValue;
+    llb_launch(gla_chunk_prefix_kernel, dim3((n_state + 255) / 256, B), dim3(256), 0, stream, tmp, state, seq_chunk0, chunk_len,
+               seq_slot, head_decay, per_head, n_state);
+    return llb_status();
+}
+
 // out[t, h * dv + d] = o[t, h, d] / sqrt(mean_d o[t, h, :]^2 + eps) * w[d] * silu(g[t, h * dv + d])      (gate_act 1: sigmoid(g))
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) gla_out_kernel(const float* __restrict__ o, const T* __restrict__ g, int g_stride,

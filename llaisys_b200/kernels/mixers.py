@@ -57,6 +57,44 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: Optional[torch.Ten
     return out
 
 
+SCAN_CHUNK = 64               # tokens of a chunk of a long step of the constant-decay recurrence
+SCAN_CHUNKED_FROM = 256       # steps whose longest sequence brings at least this many tokens run chunk by chunk
+
+
+def scan_chunks(n_new, device, chunk: int = SCAN_CHUNK):
+    """The chunks of a step whose sequences bring n_new[b] tokens: int32 device tensors chunk_start [NC + 1] (first packed
+    token of every chunk), chunk_len [NC], seq_chunk0 [B + 1] (first chunk of every sequence), chunk_row [NC] (0 .. NC - 1)."""
+    starts, lens, seq0, at = [], [], [0], 0
+    for n in n_new:
+        for c0 in range(0, n, chunk):
+            starts.append(at + c0)
+            lens.append(min(chunk, n - c0))
+        at += n
+        seq0.append(len(starts))
+    starts.append(at)
+    flat = torch.tensor(starts + lens + seq0 + list(range(len(lens))), dtype=torch.int32).to(device)
+    nc, b = len(lens), len(n_new)
+    return flat[:nc + 1], flat[nc + 1:2 * nc + 1], flat[2 * nc + 1:2 * nc + 2 + b], flat[2 * nc + 2 + b:]
+
+
+def gla_scan_chunked(proj: torch.Tensor, H: int, dk: int, dv: int, state: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+                     head_decay: torch.Tensor, chunks, act: Optional[str] = None) -> torch.Tensor:
+    """The constant-decay recurrence (gla_scan with head_decay) of a long step, its chunks side by side: the recurrence over
+    every chunk from a zero state, one pass that turns the chunks' local states into the states they start with (and
+    leaves the sequences' states as the step ends them), and the recurrence over every chunk again.  chunks: scan_chunks()
+    of the step.  Returns o [T, H dv] in float32; differs from the token-by-token walk by float32 rounding only."""
+    chunk_start, chunk_len, seq_chunk0, chunk_row = chunks
+    nc = chunk_len.numel()
+    n_state = H * dk * dv
+    tmp = torch.zeros((nc, n_state), dtype=torch.float32, device=proj.device)
+    gla_scan(proj, H, dk, dv, None, tmp, chunk_start, chunk_row, nc, 1.0, 1.0, head_decay=head_decay, act=act)
+    f = _fn(load_module("gla.cu"), "llb_gla_chunk_prefix", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                           c_int, c_void_p])
+    _check(f(_ptr(tmp), _ptr(state), _ptr(seq_chunk0), _ptr(chunk_len), _ptr(seq_slot), _ptr(head_decay), dk * dv, n_state, n_seqs,
+             _stream()), "constant-decay recurrence (chunks' starting states)")
+    return gla_scan(proj, H, dk, dv, None, tmp, chunk_start, chunk_row, nc, 1.0, 1.0, head_decay=head_decay, act=act)
+
+
 def gla_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, H: int, dv: int, eps: float,
             out_dtype: torch.dtype, gate_act: str = "silu") -> torch.Tensor:
     """[T, H dv]: every head's o (float32) RMS-normed over its dv channels with `weight` [dv], times silu(gate) (gate a

@@ -213,7 +213,9 @@ class LightningAttention(Mixer):
     (heads x value_dim); per head S <- decay_h S + k v^T, o = S^T q, with S [key_dim, value_dim] in float32 in the cache's
     fixed-size state of the sequence (zero at its start).  The heads' results, side by side, are RMS-normed together with
     one weight over all of them, multiplied by sigmoid(Wg h) and projected.  q, k and v leave their product in float32;
-    the recurrence is the kernel of the gated linear attention with the decay taken from a table per head.
+    the recurrence is the kernel of the gated linear attention with the decay taken from a table per head.  A step in which
+    some sequence brings 256 tokens or more runs in chunks of 64 tokens side by side (kernels.gla_scan_chunked): with a
+    constant decay a chunk's effect on the state is a^n S + (what the chunk reaches from zero).
 
     params: hidden_size, num_heads, key_dim, value_dim, decay (one number per head), eps, names (q, k, v, g, o, norm)."""
     capturable = True
@@ -251,8 +253,20 @@ class LightningAttention(Mixer):
     def forward(self, x, ctx, call):
         qkv = kernels.linear(x, self.w_in, out_dtype=torch.float32)
         gate = kernels.linear(x, self.w_gate)
-        o = kernels.gla_scan(qkv, self.nh, self.dk, self.dv, None, ctx.state(call), ctx.seq_start, ctx.seq_slot, ctx.n_seqs,
-                             1.0, 1.0, head_decay=self.decay, act="silu")
+        n_new = getattr(ctx, "n_new", None)
+        if n_new and max(n_new) >= kernels.mixers.SCAN_CHUNKED_FROM:
+            chunks = getattr(ctx, "_scan_chunks", None)          # one plan per step, shared by the step's layers
+            if chunks is None:
+                chunks = kernels.scan_chunks(n_new, x.device)
+                try:
+                    ctx._scan_chunks = chunks
+                except AttributeError:
+                    pass
+            o = kernels.gla_scan_chunked(qkv, self.nh, self.dk, self.dv, ctx.state(call), ctx.seq_slot, ctx.n_seqs, self.decay,
+                                         chunks, act="silu")
+        else:
+            o = kernels.gla_scan(qkv, self.nh, self.dk, self.dv, None, ctx.state(call), ctx.seq_start, ctx.seq_slot, ctx.n_seqs,
+                                 1.0, 1.0, head_decay=self.decay, act="silu")
         y = kernels.gla_out(o, gate, self.w_norm, 1, self.nh * self.dv, self.eps, x.dtype, gate_act="sigmoid")
         return kernels.linear(y, self.w_o, out_dtype=torch.float32)
 

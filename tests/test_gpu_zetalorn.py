@@ -151,8 +151,9 @@ def test_routed_experts_with_groups_and_the_clamped_gated_activation(dtype, shap
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(24, 2, 8, 16, (0.6, 0.99)), (40, 3, 5, 7, (0.0, 1.0, 0.5)), (64, 1, 64, 64, (0.999,)), (32, 4, 32, 4, (0.9, 0.8, 0.7, 0.3))])
 def test_constant_decay_linear_attention_with_state_carried_in_slots(dtype, shape):
-    """Whole sequences, then the same sequences in portions down to single tokens, interleaved in one batch, each with its
-    state in a slot of its own; the slots hold stale numbers outside the rows that the cache clears."""
+    """Whole sequences (the long one runs in chunks side by side), then the same sequences in portions down to single
+    tokens, interleaved in one batch (long portions in chunks, short ones token by token, in one step), each with its state
+    in a slot of its own; the slots hold stale numbers outside the rows that the cache clears."""
     from llaisys_b200.config import PartSpec
     from llaisys_b200.parts import build_part
     D, H, dk, dv, decay = shape
@@ -164,7 +165,7 @@ def test_constant_decay_linear_attention_with_state_carried_in_slots(dtype, shap
                                                                  "decay": list(decay), "eps": 1e-5}), _env(dtype))
     part.load({n: _dev(v, dtype if n != "norm" else torch.float32) for n, v in w.items()})
     assert part.state_size() == H * dk * dv
-    seqs = [_bf16_exact(rng.normal(size=(n, D))) for n in (150, 1, 23)]
+    seqs = [_bf16_exact(rng.normal(size=(n, D))) for n in (700, 1, 23)]
     m = {"heads": H, "dim": dk, "vdim": dv, "decay": list(decay)}
     want = [plain.lightning_attention(s, w, m, 1e-5) for s in seqs]
     state = torch.full((6, H * dk * dv), 7.0, dtype=torch.float32, device=DEV)
@@ -173,11 +174,12 @@ def test_constant_decay_linear_attention_with_state_carried_in_slots(dtype, shap
     def step(who, parts_):
         x = np.concatenate(parts_)
         starts = np.concatenate([[0], np.cumsum([len(p) for p in parts_])])
-        ctx = SimpleNamespace(state=lambda call: state, seq_start=_i32(starts), seq_slot=_i32([slots[i] for i in who]), n_seqs=len(who))
+        ctx = SimpleNamespace(state=lambda call: state, seq_start=_i32(starts), seq_slot=_i32([slots[i] for i in who]), n_seqs=len(who),
+                              n_new=[len(p) for p in parts_])
         out = part.forward(_dev(x, dtype), ctx, 0).float().cpu().numpy()
         return [out[starts[j]:starts[j + 1]] for j in range(len(who))]
 
-    for plans in ([[150], [1], [23]], [[3, 1, 1, 79, 2, 64], [0, 1], [1, 2, 17, 1, 2]], [[65, 85], [0, 1], [0, 23]]):
+    for plans in ([[700], [1], [23]], [[3, 1, 1, 301, 2, 328, 64], [0, 1], [1, 2, 17, 1, 2]], [[65, 635], [0, 1], [0, 23]]):
         for s in slots:
             state[s].zero_()
         got, fed = [[] for _ in seqs], [0] * len(seqs)
