@@ -14,6 +14,11 @@
 // `kv_row_stride` > 0: the step's own keys (and values) stand in a buffer of their own with that row stride.
 // `dist_r1`, `dist_r2` (two numbers per query head): a score loses r1 ln(1 + r2 (p - t)), a penalty that grows with the
 // distance.  `q_temp_every` > 0: the query at position p is multiplied by 1 + q_temp_coef ln(floor((p + 1) / every) + 1).
+// `chunk` C > 0: the query at position p sees no key before floor(p / C) * C.  `maps` M > 1: M key heads share one value
+// head (several score maps over one set of values) and a cache key row holds their keys side by side.  `pool` P > 0 (with a
+// window W): beside the window's keys, one key and value per block of P positions that lies wholly before the window
+// (block b is seen from p when b P + P - 1 <= p - W), read at row b of a second cache and walked before the window's tiles;
+// tokens and blocks share one softmax.  `out_f32`: the result is float32 whatever the operands are.
 //
 // Keys are walked in tiles of one cache page with an online softmax, so nothing of size
 // [queries, keys] is ever stored.

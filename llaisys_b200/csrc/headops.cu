@@ -137,10 +137,9 @@ __global__ void __launch_bounds__(128) pool_append_kernel(PoolAppendParams p) {
     if (blk >= (before + n_new) / p.pool) return;
     const int* table = p.page_table + (size_t)b * p.table_stride;
     const int* ptable = p.ptable + (size_t)b * p.ptable_stride;
-    const int per = p.dk + p.dv;
+    const int per = p.dk + p.dv, h = blockIdx.z;               // a block per (block of positions, sequence, head)
     const float inv = 1.0f / (float)p.pool;
-    for (int i = threadIdx.x; i < p.kv_heads * per; i += blockDim.x) {
-        const int h = i / per, j = i - h * per;
+    for (int j = threadIdx.x; j < per; j += blockDim.x) {
         const bool is_k = j < p.dk;
         const int e = is_k ? j : j - p.dk, w = is_k ? p.dk : p.dv;
         const T* fresh = (const T*)(is_k ? p.k_new : p.v_new);
@@ -159,8 +158,8 @@ __global__ void __launch_bounds__(128) pool_append_kernel(PoolAppendParams p) {
 LLB_API int llb_pool_append(PoolAppendParams p, int dtype, int B, int max_new, cudaStream_t stream) {
     if (B == 0 || max_new == 0) return 0;
     if (p.pool <= 0 || p.kv_heads <= 0) return (int)cudaErrorInvalidValue;
-    dim3 grid((max_new + p.pool - 1) / p.pool, B);
-    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((max_new + p.pool - 1) / p.pool, B, p.kv_heads);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     LLB_DISPATCH_DTYPE(dtype, TT, llb_launch(pool_append_kernel<TT>, grid, dim3(128), 0, stream, p));
     return llb_status();
 }

@@ -725,6 +725,11 @@ def _mma_ok(qkv, dh) -> bool:
 _decode16 = {}
 
 
+def prefill_ext_ok(qkv: torch.Tensor, dh: int, dv: int) -> bool:
+    """True when the mma.sync prefill kernel takes chunks, several score maps and pooled blocks for these operands."""
+    return _mma_ok(qkv, dh) and dv in (dh, 2 * dh)
+
+
 def decode_clusters16(dtype: torch.dtype, dh: int) -> int:
     """Clusters of sixteen blocks of the decode attention kernel that the device holds at once
     (0 where that kernel or that cluster size does not apply)."""
@@ -979,7 +984,7 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
                               window, scale, 0, extras.keep_first, extras.sink)
         return out
-    if (only_simt and not decode and dv in (dh, 2 * dh) and _mma_ok(qkv, dh) and not extras.keep_first and not extras.sink
+    if (only_simt and not decode and prefill_ext_ok(qkv, dh, dv) and not extras.keep_first and not extras.sink
             and extras.sink_logits is None and (extras.pool is None or not extras.positional())
             and not ((kpool.data_ptr() | vpool.data_ptr() | out.data_ptr()) & 15)):
         # prompts in bfloat16: the mma.sync prefill kernel with its extensions (a block owns one half of values twice as

@@ -65,6 +65,15 @@ class _NormedHeads(Mixer):
                           tables=tables, layout=self.position.pair_layout if self.position is not None else "halves",
                           tok_pos=ctx.tok_pos, append=append, err=ctx.err)
 
+    def _decode(self, ctx, common, maps: int, window, extras, splits: int):
+        """Attention of single tokens over the caches alone (their rows are appended already).  bfloat16 operands that the
+        mma.sync prefill kernel takes run there as a step of one token per sequence: a block per query head walks the
+        whole visible range on the tensor cores, which at windows of thousands of keys is several times faster than the
+        CUDA-core kernel with its key range cut into slices and a merge behind it."""
+        if kernels.prefill_ext_ok(common[0], self.dk, self.dv):
+            return kernels.attention_prefill(*common, 1, window, self.scale, all_from_cache=True, extras=extras)
+        return kernels.attention_decode(*common, window, self.scale, n_splits=splits, extras=extras)
+
     @staticmethod
     def _append_args(ctx, kv):
         return dict(tok_seq=ctx.tok_seq, seq_start=ctx.seq_start, seq_len_before=ctx.seq_len_before, kpool=kv.k, vpool=kv.v,
@@ -139,7 +148,7 @@ class DifferentialAttention(_NormedHeads):
             splits = decode_splits(ctx, 2 * self.nkvh)
             if self._kept() is not None:
                 splits = max(1, min(splits, -(-self._kept() // kernels.ops.PAGE) + 1))
-            a = kernels.attention_decode(*common, self.window, self.scale, n_splits=splits, extras=extras)
+            a = self._decode(ctx, common, 2, self.window, extras, splits)
         else:
             self._prep(proj, ctx, 2)
             a = kernels.attention_prefill(*common, ctx.max_new, self.window, self.scale, all_from_cache=False, extras=extras)
@@ -200,7 +209,7 @@ class PooledWindowAttention(_NormedHeads):
         if ctx.is_decode:
             pages = -(-self.window // kernels.ops.PAGE) + 1 + (blocks.page_table.shape[1] if blocks.page_table is not None else 0)
             splits = max(1, min(decode_splits(ctx, self.nkvh), pages))
-            a = kernels.attention_decode(*common, self.window, self.scale, n_splits=splits, extras=extras)
+            a = self._decode(ctx, common, 1, self.window, extras, splits)
         else:
             a = kernels.attention_prefill(*common, ctx.max_new, self.window, self.scale, all_from_cache=False, extras=extras)
             self._prep(proj, ctx, 1, append=self._append_args(ctx, kv), rotate=False)
