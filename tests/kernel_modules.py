@@ -12,6 +12,9 @@ TEST_MODULES = [
     *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((40, 24), (48, 40), (28, 18), (28, 20), (9, 7), (272, 264), (32, 24), (56, 40), (14, 10), (8, 6), (600, 560))],
     # attention with a distance penalty, and latent rows without a query latent (test_gpu_zedirax.py)
     *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((18, 10), (6, 14), (6, 10), (5, 3), (32, 20), (28, 12), (13, 9), (9, 5), (300, 300))],
+    # chunks, two score maps and pooled blocks (test_gpu_zetalorn.py)
+    *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((24, 8), (10, 6), (16, 8), (12, 20), (16, 32), (32, 64))],
+    ("attention_simt.cu", {"LLB_HEAD_DIM": 12}),
     # the build in which a bounded wait can be made to run out (test_gpu_kernels.py)
     ("gemm_tc.cu", {"LLB_WAIT_LIMIT": 4096, "LLB_TEST_STALL": 1}),
 ]
