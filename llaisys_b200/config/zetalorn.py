@@ -11,7 +11,7 @@
       parallel mixer    left: heads, kv_heads, dim, vdim, scale, mask: {size, pool} (window and pooled blocks),
                               rot: {dims, base, scaling} (rotation of halves)
                         right: heads, dim, vdim, decay (one number per head)
-      mlp               {kind: "moe", router: {experts, top, groups: {count, keep}}, expert: {ff, limit}}
+      mlp               {kind: "moe", router: {experts, top, groups: {count, keep}}, expert: {ff, limit}}   (groups and limit optional)
 
 Tensor names: embed, loop.step, l<i>.norm1, l<i>.norm2 (one number each), l<i>.rg1, l<i>.rg1.b, l<i>.rg2, l<i>.rg2.b,
 l<i>.mix.*, l<i>.mlp.*, final.norm, head.
@@ -151,7 +151,8 @@ def _mlp(mlp, where: str):
         if experts % count or keep > count or keep * (experts // count) < top:
             raise ConfigError(f"{where}: {experts} experts in {count} groups of which {keep} are kept cannot give {top} choices")
         groups = (count, keep)
-    return ZetalornMoE(experts, top, groups, ff=_int(ex, "ff", f"{where}.expert"), limit=_float(ex, "limit", f"{where}.expert"))
+    limit = _float(ex, "limit", f"{where}.expert") if ex.get("limit") is not None else float("inf")     # no limit: nothing is clamped
+    return ZetalornMoE(experts, top, groups, ff=_int(ex, "ff", f"{where}.expert"), limit=limit)
 
 
 @register_architecture("Zetalorn")

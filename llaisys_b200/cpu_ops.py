@@ -228,3 +228,79 @@ def route_top_softmax(logits: np.ndarray, bias, top: int, scale: float):
     zc = np.take_along_axis(z, idx, axis=-1)
     e = np.exp(zc - zc.max(axis=-1, keepdims=True))
     return idx, (e / e.sum(axis=-1, keepdims=True)) * np.float32(scale)
+
+
+def rotate_pairs(x: np.ndarray, pos_ids: np.ndarray, dims: int, base: float, factor: float = 1.0, neighbours: bool = False) -> np.ndarray:
+    """Rotation of the first `dims` elements of the last axis of x [seq, rows, d] by the angles p * base^(-2i/dims) / factor,
+    pairing element i with i + dims/2, or (neighbours) 2i with 2i + 1; angles in float64, the rest float32 (not in
+    xsmccc/llaisys)."""
+    x = x.astype(np.float32).copy()
+    half = dims // 2
+    if half == 0:
+        return x
+    f = np.power(float(base), -2.0 * np.arange(half, dtype=np.float64) / dims) / float(factor)
+    ang = np.asarray(pos_ids, dtype=np.float64)[:, None] * f[None, :]
+    cos, sin = np.cos(ang)[:, None, :].astype(np.float32), np.sin(ang)[:, None, :].astype(np.float32)
+    a, b = (slice(0, dims, 2), slice(1, dims, 2)) if neighbours else (slice(0, half), slice(half, dims))
+    u, v = x[..., a].copy(), x[..., b].copy()
+    x[..., a] = u * cos - v * sin
+    x[..., b] = v * cos + u * sin
+    return x
+
+
+def masked_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, visible: np.ndarray) -> np.ndarray:
+    """Softmax attention of q [qlen, nh, d] over k [n, nkvh, d], v [n, nkvh, dv] with a mask visible [qlen, n] given by the
+    caller (windows, chunks, blocks of keys); head h reads kv head h // (nh / nkvh) (not in xsmccc/llaisys)."""
+    qlen, nh, _ = q.shape
+    nkvh, dv = v.shape[1], v.shape[2]
+    group = nh // nkvh
+    q, k, v = q.astype(np.float32), k.astype(np.float32), v.astype(np.float32)
+    out = np.zeros((qlen, nh, dv), dtype=np.float32)
+    for h in range(nh):
+        s = np.where(visible, (q[:, h, :] @ k[:, h // group, :].T) * np.float32(scale), -np.inf)
+        e = np.where(visible, np.exp(s - s.max(axis=-1, keepdims=True)), 0.0).astype(np.float32)
+        out[:, h, :] = (e / e.sum(axis=-1, keepdims=True)) @ v[:, h // group, :]
+    return out
+
+
+def route_grouped(logits: np.ndarray, top: int, groups=None, renorm: bool = False, scale: float = 1.0):
+    """(experts [T, top], weights [T, top]): gates 1 / (1 + e^-z); with groups = (count, keep) the experts form `count` equal
+    groups of neighbours, a group's score is the sum of its two largest gates, and only experts of the `keep` best groups
+    (first maximum first) can be chosen; the `top` largest gates among them; weights gate * scale, with renorm divided by
+    the chosen gates' sum + 1e-20 (not in xsmccc/llaisys)."""
+    gate = np.float32(1.0) / (np.float32(1.0) + np.exp(-logits.astype(np.float32)))
+    T, E = gate.shape
+    choice = gate.copy()
+    if groups and groups[0] > 1:
+        count, keep = groups
+        by = gate.reshape(T, count, E // count)
+        score = np.sort(by, axis=-1)[..., ::-1][..., :2].sum(axis=-1)
+        kept = np.argsort(-score, axis=-1, kind="stable")[:, :keep]
+        allowed = np.zeros((T, count), dtype=bool)
+        np.put_along_axis(allowed, kept, True, axis=1)
+        choice = np.where(np.repeat(allowed, E // count, axis=1), choice, -np.inf)
+    idx = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    w = np.take_along_axis(gate, idx, axis=-1)
+    if renorm:
+        w = w / (w.sum(axis=-1, keepdims=True) + np.float32(1e-20))
+    return idx, w * np.float32(scale)
+
+
+def swish_clamped(gate: np.ndarray, up: np.ndarray, limit: float, alpha: float) -> np.ndarray:
+    """g = min(gate, limit), u = clamp(up, -limit, limit): g sigmoid(alpha g) (u + 1) (not in xsmccc/llaisys)."""
+    g = np.minimum(gate.astype(np.float32), np.float32(limit))
+    u = np.clip(up.astype(np.float32), np.float32(-limit), np.float32(limit))
+    return g * sigmoid(np.float32(alpha) * g) * (u + np.float32(1))
+
+
+def decayed_linear_recurrence(q: np.ndarray, k: np.ndarray, v: np.ndarray, decay: np.ndarray, state: np.ndarray) -> np.ndarray:
+    """Per head S <- decay_h S + k_t v_t^T, o_t = S^T q_t over q, k [T, H, dk], v [T, H, dv]; `state` [H, dk, dv] is
+    updated in place (not in xsmccc/llaisys)."""
+    T = q.shape[0]
+    out = np.zeros((T,) + v.shape[1:], dtype=np.float32)
+    a = decay.astype(np.float32)[:, None, None]
+    for t in range(T):
+        state *= a
+        state += k[t][:, :, None].astype(np.float32) * v[t][:, None, :].astype(np.float32)
+        out[t] = np.einsum("hkv,hk->hv", state, q[t].astype(np.float32))
+    return out

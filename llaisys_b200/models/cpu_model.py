@@ -19,9 +19,11 @@ from .. import cpu_ops
 from ..config.spec import ModelSpec, PartSpec
 
 _KNOWN = {"embedding": {"token_embedding", "scaled_pair_embedding"}, "norm": {"rms_norm"},
-          "mixer": {"gqa_attention", "windowed_sink_attention", "gated_linear_attention", "latent_attention", "min_gru"},
+          "mixer": {"gqa_attention", "windowed_sink_attention", "gated_linear_attention", "latent_attention", "min_gru",
+                    "differential_attention", "pooled_window_attention", "lightning_attention", "parallel_mixers"},
           "ffn": {"swiglu_mlp", "routed_experts", "gated_mlp"},
-          "block": {"pre_norm_residual", "parallel_residual", "sandwich_residual", "depth_averaged_residual"}, "head": {"lm_head"},
+          "block": {"pre_norm_residual", "parallel_residual", "sandwich_residual", "depth_averaged_residual", "gated_residual"},
+          "head": {"lm_head"}, "reentry": {"embedding_and_offset"},
           "position": {"rope_half_split", "rope_leading", "rope_interleaved"}}
 
 
@@ -37,9 +39,13 @@ class CpuModel:
                 self._known(sub.category, sub.part.kind)
                 if sub.norm is not None:
                     self._known("norm", sub.norm.kind)
-                pos = sub.part.params.get("position")
-                if pos is not None:
-                    self._known("position", pos.kind)
+                for part in [sub.part] + [b["part"] for b in sub.part.params.get("branches", [])]:
+                    self._known("mixer" if part is not sub.part else sub.category, part.kind)
+                    pos = part.params.get("position")
+                    if pos is not None:
+                        self._known("position", pos.kind)
+        if spec.reentry is not None:
+            self._known("reentry", spec.reentry.kind)
         self.reset()
 
     @staticmethod
@@ -142,9 +148,101 @@ class CpuModel:
         g, u = cpu_ops.linear(x, self.w[p.tensor_name(n["gate"])], b("gate")), cpu_ops.linear(x, self.w[p.tensor_name(n["up"])], b("up"))
         return cpu_ops.linear(cpu_ops.glu(g, u, p.params.get("act", "silu")), self.w[p.tensor_name(n["down"])], b("down"))
 
+    # ---- mixers with normed heads, blocks of keys, two score maps, a constant-decay recurrence
+    def _normed_rows(self, p: PartSpec, x, positions, maps: int):
+        """q [T, nh * maps, dk], k [T, nkvh * maps, dk] (normed over their elements, then rotated), v [T, nkvh, dv]."""
+        a = p.params
+        nh, nkvh, dk, dv = a["num_heads"], a["num_kv_heads"], a["key_dim"], a["value_dim"]
+        n = dict({"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm"}, **(a.get("names") or {}))
+        T = x.shape[0]
+        q = cpu_ops.linear(x, self.w[p.tensor_name(n["q"])]).reshape(T, nh * maps, dk)
+        k = cpu_ops.linear(x, self.w[p.tensor_name(n["k"])]).reshape(T, nkvh * maps, dk)
+        v = cpu_ops.linear(x, self.w[p.tensor_name(n["v"])]).reshape(T, nkvh, dv)
+        if a.get("qk_norm", True):
+            q = cpu_ops.rms_norm(q, self.w[p.tensor_name(n["q_norm"])], a.get("eps", 0.0))
+            k = cpu_ops.rms_norm(k, self.w[p.tensor_name(n["k_norm"])], a.get("eps", 0.0))
+        pos = a.get("position")
+        if pos is not None:
+            pp = pos.params
+            rot = lambda t: cpu_ops.rotate_pairs(t, positions, pp["dims"], pp["base"], pp.get("factor", 1.0), pos.kind == "rope_interleaved")
+            q, k = rot(q), rot(k)
+        return q, k, v, n
+
+    @staticmethod
+    def _kept(store, key, k, v):
+        old = store.get(key)
+        store[key] = (k, v) if old is None else (np.concatenate([old[0], k]), np.concatenate([old[1], v]))
+        return store[key]
+
+    def _differential(self, p: PartSpec, x, positions, store: dict, key):
+        a = p.params
+        nh, nkvh, dk, dv = a["num_heads"], a["num_kv_heads"], a["key_dim"], a["value_dim"]
+        q, k, v, n = self._normed_rows(p, x, positions, 2)
+        ks, vs = self._kept(store, key, k, v)
+        T, L = x.shape[0], ks.shape[0]
+        j, i = np.arange(L)[None, :], np.asarray(positions)[:, None]
+        visible = j <= i
+        if a.get("chunk"):
+            visible &= (j // a["chunk"]) == (i // a["chunk"])
+        if a.get("window"):
+            visible &= i - j < a["window"]
+        q, ks = q.reshape(T, nh, 2, dk), ks.reshape(L, nkvh, 2, dk)
+        a1 = cpu_ops.masked_attention(q[:, :, 0], ks[:, :, 0], vs, a["scale"], visible)
+        a2 = cpu_ops.masked_attention(q[:, :, 1], ks[:, :, 1], vs, a["scale"], visible)
+        l = [self.w[p.tensor_name(dict({"lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}, **(a.get("names") or {}))[t])].astype(np.float32)
+             for t in ("lq1", "lk1", "lq2", "lk2")]
+        lam = np.exp((l[0] * l[1]).sum()) - np.exp((l[2] * l[3]).sum()) + np.float32(a["diff"])
+        o = a1 - np.float32(lam) * a2
+        o = cpu_ops.rms_norm(o, np.ones(dv, dtype=np.float32), a.get("eps", 0.0)) * np.float32(1.0 - a["diff"])
+        return cpu_ops.linear(o.reshape(T, nh * dv), self.w[p.tensor_name(n["o"])])
+
+    def _pooled_window(self, p: PartSpec, x, positions, store: dict, key):
+        a = p.params
+        nh, dv, W, P = a["num_heads"], a["value_dim"], a["window"], a["pool"]
+        q, k, v, n = self._normed_rows(p, x, positions, 1)
+        ks, vs = self._kept(store, key, k, v)
+        T, L = x.shape[0], ks.shape[0]
+        nb = L // P
+        kb = ks[:nb * P].reshape(nb, P, *ks.shape[1:]).mean(axis=1, dtype=np.float32)
+        vb = vs[:nb * P].reshape(nb, P, *vs.shape[1:]).mean(axis=1, dtype=np.float32)
+        i = np.asarray(positions)[:, None]
+        j, b = np.arange(L)[None, :], np.arange(nb)[None, :]
+        visible = np.concatenate([(j <= i) & (i - j < W), b * P + P - 1 <= i - W], axis=1)
+        o = cpu_ops.masked_attention(q, np.concatenate([ks, kb]), np.concatenate([vs, vb]), a["scale"], visible)
+        return cpu_ops.linear(o.reshape(T, nh * dv), self.w[p.tensor_name(n["o"])])
+
+    def _lightning(self, p: PartSpec, x, store: dict, key):
+        a = p.params
+        H, dk, dv = a["num_heads"], a["key_dim"], a["value_dim"]
+        n = dict({"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}, **(a.get("names") or {}))
+        w = lambda t: self.w[p.tensor_name(n[t])]
+        T = x.shape[0]
+        silu = lambda t: t * cpu_ops.sigmoid(t)
+        q, k = silu(cpu_ops.linear(x, w("q"))).reshape(T, H, dk), silu(cpu_ops.linear(x, w("k"))).reshape(T, H, dk)
+        v = silu(cpu_ops.linear(x, w("v"))).reshape(T, H, dv)
+        if key not in store:
+            store[key] = np.zeros((H, dk, dv), dtype=np.float32)
+        o = cpu_ops.decayed_linear_recurrence(q, k, v, np.asarray(a["decay"], dtype=np.float32), store[key]).reshape(T, H * dv)
+        o = cpu_ops.rms_norm(o, w("norm"), a["eps"]) * cpu_ops.sigmoid(cpu_ops.linear(x, w("g")))
+        return cpu_ops.linear(o, w("o"))
+
+    def _mixer_of(self, part: PartSpec, h, positions, store, key):
+        if part.kind == "differential_attention":
+            return self._differential(part, h, positions, store, key)
+        if part.kind == "pooled_window_attention":
+            return self._pooled_window(part, h, positions, store, key)
+        if part.kind == "lightning_attention":
+            return self._lightning(part, h, store, key)
+        a = part.params                                            # parallel_mixers
+        outs = [self._mixer_of(b["part"], h, positions, store, (key, i)) for i, b in enumerate(a["branches"])]
+        ws = [self.w[part.tensor_name(b["out"])] for b in a["branches"]]
+        return sum(cpu_ops.rms_norm(o, w, a["eps"]) for o, w in zip(outs, ws)) * np.float32(1.0 / len(outs))
+
     def _part(self, sub, h, positions, store, m, owner):
         """One part's output for normed input h."""
         kind = sub.part.kind
+        if kind in ("differential_attention", "pooled_window_attention", "lightning_attention", "parallel_mixers"):
+            return self._mixer_of(sub.part, h, positions, store, m)
         if kind == "gated_linear_attention":
             return self._gla(sub.part, h, store, m)
         if kind == "min_gru":
@@ -205,15 +303,27 @@ class CpuModel:
         n = {"router": "router", "bias": "correction", "expert_up": "e{e}.up", "expert_down": "e{e}.down",
              "shared_up": "shared.up", "shared_down": "shared.down", "shared_gate": "shared.sg", **(a.get("names") or {})}
         bias = self.w[p.tensor_name(n["bias"])] if a.get("use_bias", True) else None
-        top_of = cpu_ops.route_top_softmax if a.get("gate") == "softmax_chosen" else cpu_ops.route_top
-        idx, wgt = top_of(cpu_ops.linear(x, self.w[p.tensor_name(n["router"])]), bias, a["top"], a.get("route_scale", 1.0))
+        logits = cpu_ops.linear(x, self.w[p.tensor_name(n["router"])])
+        if a.get("groups") or a.get("renorm"):
+            g = a.get("groups")
+            idx, wgt = cpu_ops.route_grouped(logits, a["top"], (g["count"], g["keep"]) if g else None, bool(a.get("renorm")),
+                                             a.get("route_scale", 1.0))
+        else:
+            top_of = cpu_ops.route_top_softmax if a.get("gate") == "softmax_chosen" else cpu_ops.route_top
+            idx, wgt = top_of(logits, bias, a["top"], a.get("route_scale", 1.0))
         act = cpu_ops.gelu if a.get("act") == "gelu" else cpu_ops.relu_squared
+        gated = a.get("act") == "swish_clamped"
         out = np.zeros((x.shape[0], a["hidden_size"]), dtype=np.float32)
         for t in range(x.shape[0]):
             for e, wt in zip(idx[t], wgt[t]):
                 up = self.w[p.tensor_name(n["expert_up"].format(e=int(e)))]
                 down = self.w[p.tensor_name(n["expert_down"].format(e=int(e)))]
-                out[t] += wt * cpu_ops.linear(act(cpu_ops.linear(x[t:t + 1], up)), down)[0]
+                if gated:
+                    gate = self.w[p.tensor_name(n.get("expert_gate", "e{e}.gate").format(e=int(e)))]
+                    y = cpu_ops.swish_clamped(cpu_ops.linear(x[t:t + 1], gate), cpu_ops.linear(x[t:t + 1], up), a["limit"], a.get("alpha", 1.0))
+                else:
+                    y = act(cpu_ops.linear(x[t:t + 1], up))
+                out[t] += wt * cpu_ops.linear(y, down)[0]
         if a.get("shared_ff"):
             shared = cpu_ops.linear(act(cpu_ops.linear(x, self.w[p.tensor_name(n["shared_up"])])), self.w[p.tensor_name(n["shared_down"])])
             if a.get("shared_gate"):
@@ -252,8 +362,15 @@ class CpuModel:
         """Feeds the next tokens of the sequence; returns float32 logits [len(tokens), vocab]."""
         positions = np.arange(self.length, self.length + len(tokens))
         x = self._embed(tokens)
+        first = x                                          # looped layers: the embedding's output joins again before later passes
         results = [x]                                      # depth-averaged layers: the embedding's output and every layer's result
         for c, call in enumerate(self.spec.order):
+            if call.opens_pass is not None:
+                re = self.spec.reentry
+                offsets = self.w[re.tensor_name(re.params.get("tensor", "offset"))].astype(np.float32)
+                if call.opens_pass > 0:
+                    x = cpu_ops.add(x, first)
+                x = cpu_ops.add(x, np.broadcast_to(offsets[call.opens_pass], x.shape))
             owner = self.cache[call.cache_of] if call.cache_of is not None else None
             m = 0
             layer = self.spec.layers[call.layer]
@@ -269,6 +386,10 @@ class CpuModel:
                     y = self._norm(sub.post_norm, y) * np.float32(layer.params.get("mult", 1.0))
                 elif layer.block == "depth_averaged_residual":
                     y = y * np.float32(layer.params.get("mult", 1.0))
+                elif layer.block == "gated_residual":          # the part's output passes a gate computed from the same input
+                    g = layer.params["gates"][layer.sublayers.index(sub)]
+                    prefix = layer.params.get("prefix", "")
+                    y = y * cpu_ops.sigmoid(cpu_ops.linear(h, self.w[f"{prefix}.{g}"], self.w[f"{prefix}.{g}.b"]))
                 x = cpu_ops.add(y, x)
             if layer.block == "depth_averaged_residual":     # what goes on is a weighted sum of all results so far
                 results.append(x)
@@ -278,7 +399,7 @@ class CpuModel:
         x = self._norm(self.spec.final_norm, x)
         head = self.spec.head
         name = head.params.get("tied_to") or head.tensor_name(head.params.get("tensor", "weight"))
-        return cpu_ops.linear(x, self.w[name])
+        return cpu_ops.linear(x, self.w[name]) * np.float32(head.params.get("scale", 1.0))
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int, stop_ids: Sequence[int] = ()) -> List[int]:
         """Greedy continuation: the new tokens (a stop token included)."""

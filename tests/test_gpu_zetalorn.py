@@ -470,7 +470,8 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(tmp_path):
 
 
 def test_command_line(tmp_path):
-    """python -m llaisys_b200.cli on a model folder of this design and on a configuration with random weights."""
+    """python -m llaisys_b200.cli on a model folder of this design and on a configuration with random weights; --test
+    compares the engine's tokens with those of the package's CPU model."""
     import os
     import sys
     env = dict(os.environ, PYTHONPATH=str(ROOT))
@@ -478,17 +479,17 @@ def test_command_line(tmp_path):
     oracle = zh.Oracle(folder)
     (tmp_path / "batch.txt").write_text("5,17,3,200,7,7,7,7,7\n[9, 8]\n1\n")
     out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folder), "--batch-file", str(tmp_path / "batch.txt"),
-                          "--max_steps", "6", "--dtype", "float32", "--top_k", "1"], env=env, capture_output=True, text=True, timeout=600)
+                          "--max_steps", "6", "--dtype", "float32", "--test"], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
-    assert out.stdout.count("Tokens:") == 3
+    assert out.stdout.count("Tokens:") == 3 and "Test passed" in out.stdout
     want = [5, 17, 3, 200, 7, 7, 7, 7, 7] + _greedy(oracle, [5, 17, 3, 200, 7, 7, 7, 7, 7], 6)
     assert str(want) in out.stdout or ", ".join(map(str, want)) in out.stdout, out.stdout[-1500:]
     cfg = tmp_path / "cfg.json"
     cfg.write_text(json.dumps(zh.CONFIGS["Q"]))
     out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--random-weights", str(cfg), "--seed", "3", "--tokens", "1,2,3",
-                          "--max_steps", "4", "--dtype", "bfloat16"], env=env, capture_output=True, text=True, timeout=600)
+                          "--max_steps", "4", "--dtype", "float32", "--test"], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
-    assert "Tokens:" in out.stdout
+    assert "Tokens:" in out.stdout and "Test passed" in out.stdout
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -218,3 +218,20 @@ def test_the_first_token_reaches_the_last_through_blocks_and_state_only():
         if silent.endswith("right.o"):
             # positions 6 .. 8: the first token has left the window and its block (positions 0 .. 3) is not seen yet
             assert moved[:6].min() > 0 and moved[6:lo].max() == 0.0 and moved[lo] > 0, moved[:12]
+
+
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
+def test_cpu_model_against_the_plain_implementation(tmp_path, name):
+    """The package's CPU model (float32 operators, a cache, the prompt and then single tokens) against the plain float64
+    evaluation of whole sequences: whole prompts, and the same tokens fed in portions down to single ones."""
+    from llaisys_b200.models.cpu_model import CpuModel
+    cfg = zh.CONFIGS[name]
+    folder = zh.make_folder(tmp_path, cfg, seed=4, gain=4.0)
+    oracle = zh.Oracle(folder)
+    toks = zh.random_requests(cfg, [90], seed=7)[0]
+    ref = oracle.logits(toks)
+    model = CpuModel.from_folder(folder)
+    assert np.abs(model.step(toks) - ref).max() < 2e-4
+    model.reset()
+    got = np.concatenate([model.step(toks[:70]), model.step(toks[70:72])] + [model.step([t]) for t in toks[72:]])
+    assert np.abs(got - ref).max() < 2e-4
