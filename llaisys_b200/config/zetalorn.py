@@ -8,9 +8,11 @@
     layers          list of {type: "attention" | "parallel", mixer: {...}, mlp: {...} or null}
       attention mixer   heads, kv_heads, dim (query/key size of one score map), vdim, scale, diff, mask: {size} (chunks),
                         rot: {dims, base, scaling: {factor}} (rotation of neighbouring pairs; scaling optional)
-      parallel mixer    left: heads, kv_heads, dim, vdim, scale, mask: {size, pool} (window and pooled blocks),
+      parallel mixer    left: heads, kv_heads, dim, vdim, scale, mask: {size, pool} (window and pooled blocks; without
+                              `pool` what has left the window is not seen),
                               rot: {dims, base, scaling} (rotation of halves)
-                        right: heads, dim, vdim, decay (one number per head)
+                        right: heads, dim, vdim, decay (one number per head, or one for all)
+                        (vdim absent: as wide as dim)
       mlp               {kind: "moe", router: {experts, top, groups: {count, keep}}, expert: {ff, limit}}   (groups and limit optional)
 
 Tensor names: embed, loop.step, l<i>.norm1, l<i>.norm2 (one number each), l<i>.rg1, l<i>.rg1.b, l<i>.rg2, l<i>.rg2.b,
@@ -108,7 +110,8 @@ def _heads(m: dict, where: str):
     heads, kv_heads = _int(m, "heads", where), _int(m, "kv_heads", where)
     if heads % kv_heads:
         raise ConfigError(f"{where}: {heads} query heads cannot share {kv_heads} key/value heads")
-    return heads, kv_heads, _int(m, "dim", where), _int(m, "vdim", where), _float(m, "scale", where, positive=False)
+    dim = _int(m, "dim", where)
+    return heads, kv_heads, dim, (_int(m, "vdim", where) if m.get("vdim") is not None else dim), _float(m, "scale", where, positive=False)
 
 
 def _mixer(kind, m: dict, where: str):
@@ -122,13 +125,17 @@ def _mixer(kind, m: dict, where: str):
         heads, kv_heads, dim, vdim, scale = _heads(l, f"{where}.left")
         mask = _dict(l, "mask", f"{where}.left")
         left = ZetalornWindowed(heads, kv_heads, dim, vdim, scale, window=_int(mask, "size", f"{where}.left.mask"),
-                                pool=_int(mask, "pool", f"{where}.left.mask"), rot=_rotation(l, f"{where}.left", dim))
+                                pool=_int(mask, "pool", f"{where}.left.mask") if mask.get("pool") is not None else 0,
+                                rot=_rotation(l, f"{where}.left", dim))
         rh = _int(r, "heads", f"{where}.right")
         decay = r.get("decay")
+        if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+            decay = [decay] * rh                                   # one number for all heads
         if not isinstance(decay, list) or len(decay) != rh or any(isinstance(d, bool) or not isinstance(d, (int, float)) or not (0 <= d <= 1)
                                                                   for d in decay):
             raise ConfigError(f"{where}.right: 'decay' must list one number in [0, 1] for each of the {rh} heads, got {decay!r}")
-        right = ZetalornLinear(rh, _int(r, "dim", f"{where}.right"), _int(r, "vdim", f"{where}.right"), tuple(float(d) for d in decay))
+        rd = _int(r, "dim", f"{where}.right")
+        right = ZetalornLinear(rh, rd, _int(r, "vdim", f"{where}.right") if r.get("vdim") is not None else rd, tuple(float(d) for d in decay))
         return ZetalornParallel(left, right)
     raise ConfigError(f"{where}: the mixers of this architecture are 'attention' and 'parallel', got {kind!r}")
 

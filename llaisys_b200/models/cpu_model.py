@@ -198,10 +198,11 @@ class CpuModel:
 
     def _pooled_window(self, p: PartSpec, x, positions, store: dict, key):
         a = p.params
-        nh, dv, W, P = a["num_heads"], a["value_dim"], a["window"], a["pool"]
+        nh, dv, W, P = a["num_heads"], a["value_dim"], a["window"], a.get("pool") or 0
         q, k, v, n = self._normed_rows(p, x, positions, 1)
         ks, vs = self._kept(store, key, k, v)
         T, L = x.shape[0], ks.shape[0]
+        P = P or L + 1                                             # no pool: no block is ever complete
         nb = L // P
         kb = ks[:nb * P].reshape(nb, P, *ks.shape[1:]).mean(axis=1, dtype=np.float32)
         vb = vs[:nb * P].reshape(nb, P, *vs.shape[1:]).mean(axis=1, dtype=np.float32)

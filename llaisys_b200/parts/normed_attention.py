@@ -170,20 +170,24 @@ class PooledWindowAttention(_NormedHeads):
     of block rows (one per P tokens, all kept) that kernels.pool_append fills as blocks complete, before the step's
     attention runs.
 
+    Without a pool (0 or absent) the mixer is a plain sliding window with normed and rotated heads and one user of the cache.
+
     params: hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale, window, pool, eps, qk_norm, position, names."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         p = spec.params
         self._common(p)
-        self.window, self.pool = int(p["window"]), int(p["pool"])
-        if self.window <= 0 or self.pool <= 0:
-            raise ValueError(f"window {self.window} and pool {self.pool} must be positive")
+        self.window, self.pool = int(p["window"]), int(p.get("pool") or 0)          # pool 0: no blocks, a plain window
+        if self.window <= 0 or self.pool < 0:
+            raise ValueError(f"window {self.window} must be positive and pool {self.pool} not negative")
 
     def kv_need(self):
         return KVNeed(self.nkvh, self.dk, self.dv, max(self.window, self.pool))
 
     def cache_users(self):
+        if not self.pool:
+            return [(self.kv_need(), 0)]
         return [(self.kv_need(), 0), (KVNeed(self.nkvh, self.dk, self.dv, None, every=self.pool), 0)]
 
     def tensors(self):
@@ -196,18 +200,19 @@ class PooledWindowAttention(_NormedHeads):
         self._load_norms(tensors)
 
     def forward(self, x, ctx, call):
-        kv, blocks = ctx.kv(call), ctx.kv(call + 1)
+        kv, blocks = ctx.kv(call), (ctx.kv(call + 1) if self.pool else None)
         proj = kernels.linear(x, self.w_in)
         # single tokens: norm, rotation and append in one launch (the ring still holds the block's earlier positions);
         # longer steps append after the attention, so that the ring is not overwritten under the step's own queries
         self._prep(proj, ctx, 1, append=self._append_args(ctx, kv) if ctx.is_decode else None)
-        kernels.pool_append(proj, self.nh * self.dk, self.nkvh, self.dk, self.dv, self.pool, kv, blocks, ctx.seq_start,
-                            ctx.seq_len_before, ctx.n_seqs, ctx.max_new)
-        extras = kernels.AttnExtras(value_dim=self.dv, pinned=kv.pinned, pool=(self.pool, blocks))
+        if self.pool:
+            kernels.pool_append(proj, self.nh * self.dk, self.nkvh, self.dk, self.dv, self.pool, kv, blocks, ctx.seq_start,
+                                ctx.seq_len_before, ctx.n_seqs, ctx.max_new)
+        extras = kernels.AttnExtras(value_dim=self.dv, pinned=kv.pinned, pool=(self.pool, blocks) if self.pool else None)
         common = (proj, self.nh, self.nkvh, self.dk, kv.k, kv.v, kv.page_table, kv.ring, ctx.seq_start, ctx.seq_len_before,
                   ctx.n_seqs)
         if ctx.is_decode:
-            pages = -(-self.window // kernels.ops.PAGE) + 1 + (blocks.page_table.shape[1] if blocks.page_table is not None else 0)
+            pages = -(-self.window // kernels.ops.PAGE) + 1 + (blocks.page_table.shape[1] if blocks is not None else 0)
             splits = max(1, min(decode_splits(ctx, self.nkvh), pages))
             a = self._decode(ctx, common, 1, self.window, extras, splits)
         else:

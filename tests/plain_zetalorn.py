@@ -71,7 +71,7 @@ def differential_attention(h, w, m, eps, pos=None):
     """The mixer of an 'attention' layer.  w: the layer's mixer tensors by local name; m: its 'mixer' object."""
     T = h.shape[0]
     pos = np.arange(T) if pos is None else pos
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
     q = (h @ w["q"].T).reshape(T, H * 2, d)
     k = (h @ w["k"].T).reshape(T, G * 2, d)
     v = (h @ w["v"].T).reshape(T, G, dv)
@@ -81,7 +81,7 @@ def differential_attention(h, w, m, eps, pos=None):
     factor = (rot.get("scaling") or {}).get("factor", 1.0)
     q = rotate(q, pos, rot.get("dims", 0), rot.get("base", 1.0), factor, "neighbours").reshape(T, H, 2, d)
     k = rotate(k, pos, rot.get("dims", 0), rot.get("base", 1.0), factor, "neighbours").reshape(T, G, 2, d)
-    visible = chunk_mask(T, m["mask"]["size"])
+    visible = chunk_mask(T, (m.get("mask") or {}).get("size") or T + 1)          # no mask: one chunk
     lam = np.exp((w["lq1"] * w["lk1"]).sum()) - np.exp((w["lq2"] * w["lk2"]).sum()) + m["diff"]
     out = np.zeros((T, H, dv))
     for hd in range(H):
@@ -99,7 +99,7 @@ def pooled_window_attention(h, w, m, eps):
     """The left half of a 'parallel' mixer: a sliding window over tokens plus one mean key and value for every block
     of `pool` tokens that lies wholly before the window, in one softmax."""
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
     q = rms((h @ w["q"].T).reshape(T, H, d), eps) * w["q.norm"]
     k = rms((h @ w["k"].T).reshape(T, G, d), eps) * w["k.norm"]
     v = (h @ w["v"].T).reshape(T, G, dv)
@@ -107,7 +107,7 @@ def pooled_window_attention(h, w, m, eps):
     factor = (rot.get("scaling") or {}).get("factor", 1.0)
     q = rotate(q, np.arange(T), rot.get("dims", 0), rot.get("base", 1.0), factor, "halves")
     k = rotate(k, np.arange(T), rot.get("dims", 0), rot.get("base", 1.0), factor, "halves")
-    W, P = m["mask"]["size"], m["mask"]["pool"]
+    W, P = m["mask"]["size"], m["mask"].get("pool") or T + 1          # no pool: no block is ever complete
     nb = T // P
     kb = k[:nb * P].reshape(nb, P, G, d).mean(axis=1)
     vb = v[:nb * P].reshape(nb, P, G, dv).mean(axis=1)
@@ -124,11 +124,11 @@ def pooled_window_attention(h, w, m, eps):
 def lightning_attention(h, w, m, eps):
     """The right half of a 'parallel' mixer: per head S <- decay S + k v^T, o = S^T q, token after token."""
     T = h.shape[0]
-    H, d, dv = m["heads"], m["dim"], m["vdim"]
+    H, d, dv = m["heads"], m["dim"], m.get("vdim", m["dim"])
     q = silu(h @ w["q"].T).reshape(T, H, d)
     k = silu(h @ w["k"].T).reshape(T, H, d)
     v = silu(h @ w["v"].T).reshape(T, H, dv)
-    decay = np.asarray(m["decay"], dtype=np.float64)
+    decay = np.broadcast_to(np.asarray(m["decay"], dtype=np.float64), (H,))
     S = np.zeros((H, d, dv))
     o = np.zeros((T, H, dv))
     for t in range(T):
@@ -165,6 +165,7 @@ def route(h, w_router, r):
 
 
 def expert(h, gate, up, down, limit):
+    limit = np.inf if limit is None else limit
     g = np.minimum(h @ gate.T, limit)
     u = np.clip(h @ up.T, -limit, limit)
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ down.T
@@ -175,7 +176,7 @@ def moe(h, w, mlp):
     out = np.zeros((h.shape[0], w["e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, c in zip(idx[t], wgt[t]):
-            out[t] += c * expert(h[t:t + 1], w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"], mlp["expert"]["limit"])[0]
+            out[t] += c * expert(h[t:t + 1], w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"], mlp["expert"].get("limit"))[0]
     return out
 
 

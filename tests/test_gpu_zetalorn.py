@@ -336,6 +336,27 @@ def test_the_sequences_first_tokens_and_sizes_that_are_one(tmp_path):
     compare_zl(run_tail_by_one(engine, reqs, tail=60), zh.Oracle(folder), reqs, torch.float32, ones, "ones decoded")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_what_a_configuration_leaves_out_does_not_exist(tmp_path, dtype):
+    """No pool (a plain window: what has left it is gone), one decay for all heads, values as wide as the keys, no limit on
+    the experts, no rotation, no groups, no loop: whole, decoded, in portions and through the CPU model's eyes."""
+    left = {"heads": 4, "kv_heads": 2, "dim": 16, "scale": 0.25, "mask": {"size": 40}}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": {"heads": 2, "dim": 8, "decay": 0.9}},
+             "mlp": {"kind": "moe", "router": {"experts": 4, "top": 4}, "expert": {"ff": 16}}}
+    att = {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 16, "scale": 0.25, "diff": 0.2}, "mlp": None}
+    cfg = zh.config(70, 32, [layer, att])
+    folder = zh.make_folder(tmp_path, cfg, seed=8, gain=3.0)
+    oracle = zh.Oracle(folder)
+    toks = zh.random_requests(cfg, [150, 20], seed=9)
+    engine = build_engine(folder, dtype, max_tokens=256, max_seqs=2)
+    assert len(engine.cache.group_keys) == 2 and engine.cache.every == [1, 1]
+    compare_zl(run_whole(engine, toks), oracle, toks, dtype, cfg, "whole")
+    compare_zl(run_tail_by_one(engine, toks, tail=100), oracle, toks, dtype, cfg, "decoded")
+    compare_zl(run_chunked(engine, toks, [63, 2, 65]), oracle, toks, dtype, cfg, "portions")
+    from llaisys_b200.models.cpu_model import CpuModel
+    assert np.abs(CpuModel.from_folder(folder).step(toks[1]) - oracle.logits(toks[1])).max() < 2e-4
+
+
 # ----------------------------------------------------------------------------- whole models under every schedule
 class Model:
     def __init__(self, name, tmp):

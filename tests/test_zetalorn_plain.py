@@ -34,6 +34,16 @@ def test_configuration_is_read_and_turned_into_a_spec():
     assert q.loop is None and q.logit_scale == 1.0 and q.to_spec().reentry is None
     assert len(q.to_spec().layers[1].sublayers) == 1 and q.to_spec().layers[1].params["gates"] == ["rg1"]
     assert q.to_dict() == zh.CONFIGS["Q"]
+    # what a configuration leaves out does not exist: no pool (a plain window, one user of the cache), one decay for all heads,
+    # values as wide as the keys, no limit on the experts' gate and up
+    def bare(c):
+        c["layers"][0]["mixer"]["left"]["mask"].pop("pool")
+        c["layers"][0]["mixer"]["left"].pop("vdim")
+        c["layers"][0]["mixer"]["right"].update(decay=0.75)
+        c["layers"][0]["mlp"]["expert"].pop("limit")
+    b = config_from_dict(zh.variant(zh.CONFIGS["P"], bare))
+    assert (b.mixers[0].left.pool, b.mixers[0].left.vdim, b.mixers[0].right.decay, b.ffs[0].limit) == (0, 16, (0.75, 0.75), float("inf"))
+    assert len(_model(zh.variant(zh.CONFIGS["P"], bare)).call_all_users[0]) == 2
 
 
 @pytest.mark.parametrize("edit, text", [
@@ -48,7 +58,7 @@ def test_configuration_is_read_and_turned_into_a_spec():
     (lambda c: c["layers"][0].update(type="conv"), "mixers"),
     (lambda c: c["loop"].update(stop=9), "loop"),
     (lambda c: c["loop"].update(start=3), "loop"),
-    (lambda c: c["layers"][0]["mixer"]["left"]["mask"].pop("pool"), "pool"),
+    (lambda c: c["layers"][0]["mixer"]["left"]["mask"].update(pool=0), "pool"),
     (lambda c: c.pop("norm"), "norm"),
 ])
 def test_configurations_that_cannot_be_are_refused(edit, text):
