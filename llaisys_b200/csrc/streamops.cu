@@ -36,7 +36,7 @@ struct StreamJoinParams {
 
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256) stream_join_kernel(StreamJoinParams p) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[8];
     const int r = blockIdx.x, H = p.H;
     llb_grid_dependency_sync();
@@ -45,18 +45,53 @@ __global__ void __launch_bounds__(256) stream_join_kernel(StreamJoinParams p) {
     const float* gate = p.gate ? p.gate + (size_t)r * p.ld_gate : nullptr;
     const float* ra = p.rows_add ? p.rows_add + (size_t)r * H : nullptr;
     const float* va = p.vec_add;
+    const bool write = delta || ra || va;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += 256) {
-        float v = x[i];
-        if (ra) v += ra[i];
-        if (va) v += va[i];
-        if (delta) {
-            const float dl = to_f32(delta[i]);
-            v += gate ? dl / (1.0f + expf(-gate[i])) : dl;
+    // four elements a thread and round where the row allows it (16-byte pieces of the float32 operands)
+    const bool vec = H % 4 == 0 && p.ld_gate % 4 == 0 &&
+                     !(((uintptr_t)p.x | (uintptr_t)p.delta | (uintptr_t)p.gate | (uintptr_t)p.rows_add | (uintptr_t)p.vec_add) & 15);
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < H; i += 1024) {
+            float4 v = *reinterpret_cast<const float4*>(x + i);
+            float* e = reinterpret_cast<float*>(&v);
+            if (ra) {
+                const float4 a = *reinterpret_cast<const float4*>(ra + i);
+                e[0] += a.x; e[1] += a.y; e[2] += a.z; e[3] += a.w;
+            }
+            if (va) {
+                const float4 a = *reinterpret_cast<const float4*>(va + i);
+                e[0] += a.x; e[1] += a.y; e[2] += a.z; e[3] += a.w;
+            }
+            if (delta) {
+                float d[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) d[u] = to_f32(delta[i + u]);
+                if (gate) {
+                    const float4 g = *reinterpret_cast<const float4*>(gate + i);
+                    const float gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) d[u] = d[u] / (1.0f + expf(-gg[u]));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) e[u] += d[u];
+            }
+            if (write) *reinterpret_cast<float4*>(x + i) = v;
+            *reinterpret_cast<float4*>(row + i) = v;
+            ss += (e[0] * e[0] + e[1] * e[1]) + (e[2] * e[2] + e[3] * e[3]);
         }
-        if (delta || ra || va) x[i] = v;
-        row[i] = v;
-        ss = fmaf(v, v, ss);
+    } else {
+        for (int i = threadIdx.x; i < H; i += 256) {
+            float v = x[i];
+            if (ra) v += ra[i];
+            if (va) v += va[i];
+            if (delta) {
+                const float dl = to_f32(delta[i]);
+                v += gate ? dl / (1.0f + expf(-gate[i])) : dl;
+            }
+            if (write) x[i] = v;
+            row[i] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     if (!p.weight) return;
     ss = block_sum_256(ss, red);
